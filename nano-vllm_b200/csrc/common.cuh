@@ -130,7 +130,7 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ------------------------------------------------------------------------------------------
-// mbarrier + bulk async copy (TMA engine, SASS: UBLKCP / SYNCS)
+// mbarrier + bulk async copy (TMA engine)
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -10,7 +10,7 @@
 //     it is cut into equal contiguous ranges, one per warp ("stream-K" over KV pages), so the
 //     load is balanced to one chunk whatever the mix of context lengths;
 //   * each warp streams its chunks through a private NSTAGES-deep ring in shared memory with
-//     1-D bulk async copies (TMA engine, cp.async.bulk -> SASS UBLKCP) completing on mbarriers;
+//     1-D bulk async copies (TMA engine, cp.async.bulk) completing on mbarriers;
 //     a (page, kv head) tile is contiguous in HBM so every copy is one linear 4 KB burst;
 //   * QK^T and PV run on the fp32 FMA pipe with all G q-heads of the kv head sharing each K/V
 //     read; softmax statistics via warp shuffles;

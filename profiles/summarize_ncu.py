@@ -44,24 +44,6 @@ def main():
                     pass
         print("   top warp stalls (avg warps stalled per issue-active cycle): " +
               ", ".join(f"{n}={v:.2f}" for v, n in sorted(stalls, reverse=True)[:8]))
-    src = page(rep, "source")
-    if len(src) > 2:
-        h = src[1]
-        n = len(h)
-        data = [r for r in src[2:] if len(r) == n]
-        iS, isrc = h.index("# Samples"), h.index("Source")
-        f = lambda x: int(x) if x.isdigit() else 0
-        tot = sum(f(r[iS]) for r in data) or 1
-        seen, out = set(), []
-        for r in sorted(data, key=lambda r: -f(r[iS])):
-            if r[isrc] in seen:
-                continue
-            seen.add(r[isrc])
-            out.append(f"   {100 * f(r[iS]) / tot:5.2f}%  {r[isrc].strip()[:100]}")
-            if len(out) == 14:
-                break
-        print("== hottest SASS (share of stall samples, duplicates across launches merged)")
-        print("\n".join(out))
 
 
 if __name__ == "__main__":
