@@ -1,0 +1,109 @@
+/*
+ * b200_mixers.h -- C ABI of libb200mix.so: sequence mixers and feed-forward pieces of hybrid decoders on B200 (sm_100a):
+ * latent attention with a softmax sink over a paged cache of compressed keys, the selective-scan recurrence with
+ * per-sequence state slots, routed experts, and the row-wise ops around them (embedding into an fp32 residual stream,
+ * residual update + weight-only layer norm, RMS norm, feed-forward activations).
+ *
+ * Conventions are those of b200_paged_attn.h: 0 or a negative B200_E* code; the caller owns every buffer; nothing
+ * synchronises the host and every launch goes to the stream passed in, so a step can be captured in a CUDA graph;
+ * per-step variation flows through device-resident metadata only.
+ *
+ * `is32` selects the activation / weight / cache element type: 0 = bf16 (serving), 1 = fp32 (everything in 32 bits).
+ * Norm statistics, softmax, router scores, the residual stream and the recurrent state are fp32 in both.
+ *
+ * Step metadata.  A varlen step (prompt portions, single tokens, or both) passes cu_q / cu_k, int32 [num_seqs + 1]
+ * cumulative counts of this step's tokens and of the tokens each sequence holds after the step, and ctx_lens = NULL.
+ * A decode step passes cu_q = cu_k = NULL and ctx_lens, int32 [num_seqs]: one token per row, ctx_lens[s] tokens after the
+ * step, 0 marking a padding row that is skipped.  Token i of a sequence with q tokens in the step and k after it sits at
+ * position k - q + i.
+ */
+#ifndef B200_MIXERS_H
+#define B200_MIXERS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "b200_paged_attn.h" /* the B200_E* codes */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int b200m_abi_version(void);
+
+/* out[i, :] = table[ids[i], :] as fp32 (the residual stream). */
+int b200m_embed(const int64_t* ids, const void* table, float* out, int n, int width, int64_t vocab, int is32, void* stream);
+
+/* x[r, :] += a[r, :] + b[r, :] + b32[r, :] (each optional; the terms are summed first), then, unless out is NULL,
+ * out[r, :] = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w.  With rows_idx (int32 [rows]) nothing is added and
+ * out[i, :] is the norm of row rows_idx[i]. */
+int b200m_add_layernorm(float* x, const void* a, const void* b, const float* b32, const void* w, void* out,
+                        const int32_t* rows_idx, int rows, int cols, float eps, int is32, void* stream);
+
+/* out = x / sqrt(mean(x^2) + eps) * w over the first `cols` elements of each (strided) row. */
+int b200m_rmsnorm(const void* x, int64_t x_stride, const void* w, void* out, int64_t out_stride, int rows, int cols,
+                  float eps, int is32, void* stream);
+
+/* kind 0: x = [gate | up] (2n per row), out = gelu_tanh(gate) * up;  1: out = relu(x)^2 (n per row);  2: silu(gate) * up. */
+int b200m_ff_act(const void* x, void* out, int64_t rows, int n, int kind, int is32, void* stream);
+
+/* ---- latent attention ---------------------------------------------------------------------------------------------- */
+
+/* Per token: cache[slot] = [ rms_norm(dkv[:rank]) * norm_w | rotate(dkv[rank : rank + rot_dim]) ].  The rotation turns the
+ * pairs (2i, 2i+1), i < rope_dims / 2, by cos_sin[position] = [cos (rope_dims/2) | sin (rope_dims/2)] (fp32, any magnitude
+ * factor folded in); elements past rope_dims pass unchanged.  slot < 0 skips the token. */
+int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, const float* cos_sin, int rope_dims,
+                       const int64_t* positions, const int32_t* slots, void* cache, int n, int rank, int rot_dim, float eps,
+                       int is32, void* stream);
+
+/* Multi-query attention of every head over the cached rows, causal, with a per-head sink logit in the softmax denominator.
+ * q_lat [H, total_q, rank]: queries already mapped into the latent space; q_raw [total_q, H, q_head_stride]: the raw query
+ * projection, whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank]. */
+int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                           const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
+                           const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
+                           int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
+                           int rot_dim, float scale, int is32, void* stream);
+
+/* ---- selective scan ------------------------------------------------------------------------------------------------ */
+
+/* Depthwise causal convolution (w [channels, taps], last tap on the current token) + bias + SiLU; the taps - 1 inputs before
+ * a portion come from conv_state [slots, taps - 1, channels] (fp32) when the sequence has tokens behind it, zeros
+ * otherwise; afterwards the slot holds the last taps - 1 inputs. */
+int b200m_causal_conv(const void* x, int64_t x_stride, const void* w, const void* bias, float* conv_state,
+                      const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, void* out,
+                      int num_seqs, int max_q, int channels, int taps, int is32, void* stream);
+
+/* S <- exp(dt A) S + dt u B;  y = (S C + D u) * silu(z), dt = softplus(dt_raw + dt_bias); A [channels, nstate] fp32;
+ * state [slots, channels, nstate] fp32, started from zero when the sequence has no tokens behind it. */
+int b200m_selective_scan(const void* u, const void* dt_raw, const void* dt_bias, const float* A, const void* Bm, const void* Cm,
+                         int64_t bc_stride, const void* Dv, const void* z, int64_t z_stride, float* state,
+                         const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, void* y,
+                         int num_seqs, int channels, int nstate, int is32, void* stream);
+
+/* ---- routed experts ------------------------------------------------------------------------------------------------ */
+
+int b200m_moe_tile_rows(void);
+
+/* idx / wgt [n, top]: the experts with the largest logits and sigmoid(logit) of each. */
+int b200m_moe_route(const float* logits, int64_t ld, int n, int num_experts, int top, int32_t* idx, float* wgt, void* stream);
+
+/* Groups the n * top (token, choice) pairs by expert, each expert's run padded to a multiple of b200m_moe_tile_rows().
+ * cap >= round_up(pairs + num_experts * (tile - 1), tile); counts: 2 * num_experts ints of scratch. */
+int b200m_moe_align(const int32_t* idx, int pairs, int num_experts, int32_t* sorted_rows, int cap, int32_t* pos_of,
+                    int32_t* tile_expert, int32_t* num_tiles, int32_t* counts, void* stream);
+
+/* C[i, :] = act(A_i . W[expert of i]^T) for every grouped row i.  gather: A_i = A[pair / top] * wgt[pair] (the expert's
+ * weighted input); else A_i = A[i].  W [experts, N, K].  act 1 = relu^2.  C is T, or fp32 when out_f32. */
+int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* sorted_rows, const float* wgt, int top, int gather,
+                   const int32_t* tile_expert, const int32_t* num_tiles, int max_tiles, const void* W, int N, int K, void* C,
+                   int out_f32, int act, int is32, void* stream);
+
+/* out[t, :] = sum_k rows[pos_of[t, k], :] + sigmoid(gate_logit[t]) * shared[t, :]  (shared optional; fp32 out). */
+int b200m_moe_combine(const float* rows, const int32_t* pos_of, int top, const void* shared, const float* gate_logit,
+                      int64_t gate_ld, float* out, int n, int width, int is32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,227 @@
+// Latent attention over a paged cache of compressed keys.
+//
+// Per token the cache holds one row [c (kv_rank, RMS-normed) | k_rot (rot_dim, rotated)] shared by all heads.  With the
+// key/value up-projections folded into the query and the output (q_lat[h] = W_uk[h]^T q_nope[h]; head output =
+// W_uv[h] * sum_j p_j c_j) attention is multi-query over those rows:
+//     s_j = (q_lat[h] . c_j + q_rot[h] . k_rot_j) * scale,   p = softmax over {s_j, j <= pos} and a per-head sink logit
+// The sink takes part in the maximum and the denominator only: it is a key with a fixed score and a zero value.
+//
+//   latent_store_kernel : RMS norm of the latent, rotation of the shared key part, scatter to the token's cache slot
+//   latent_attn_kernel  : any mix of prompt portions and single tokens (one warp per (token, head), key tiles shared
+//                         by the warps of a CTA through shared memory)
+//   latent_decode_kernel: one token per sequence, keys split over CTAs, partial (max, sum, acc) merged by the last CTA
+#include "mix_common.cuh"
+
+namespace {
+
+constexpr int LA_WARPS = 8;
+constexpr int LA_TILE = 32;
+
+// interleaved rotation of `dims` leading elements of a rot_dim-long vector; cs = [cos (dims/2) | sin (dims/2)] of the position
+__device__ __forceinline__ void rotate_pair(float u, float v, float c, float s, float& ou, float& ov) {
+    ou = u * c - v * s;
+    ov = v * c + u * s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_store_kernel(const T* __restrict__ dkv, int64_t stride, const T* __restrict__ w,
+                                                           const float* __restrict__ cos_sin, int rope_dims,
+                                                           const int64_t* __restrict__ positions, const int32_t* __restrict__ slots,
+                                                           T* __restrict__ cache, int rank, int rot_dim, float eps) {
+    B200_PDL_SYNC();
+    __shared__ float red[4];
+    const int t = blockIdx.x;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const T* x = dkv + (int64_t)t * stride;
+    T* dst = cache + (int64_t)slot * (rank + rot_dim);
+    float q = 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        const float v = ldf(x + c);
+        q = fmaf(v, v, q);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)rank + eps);
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) stf(dst + c, ldf(x + c) * rstd * ldf(w + c));
+    const float* cs = cos_sin + positions[t] * rope_dims;
+    const int half = rope_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float a, b;
+        rotate_pair(ldf(x + rank + 2 * i), ldf(x + rank + 2 * i + 1), cs[i], cs[half + i], a, b);
+        stf(dst + rank + 2 * i, a);
+        stf(dst + rank + 2 * i + 1, b);
+    }
+    for (int c = rope_dims + threadIdx.x; c < rot_dim; c += blockDim.x) stf(dst + rank + c, ldf(x + rank + c));
+}
+
+// q for one (token, head) into shared memory: [q_lat (rank) | rotated q_rot (rot_dim)], fp32, pre-multiplied by scale
+template <typename T>
+__device__ __forceinline__ void load_query(float* qs, const T* q_lat, const T* q_rot, const float* cs, int rank, int rot_dim,
+                                           int rope_dims, float scale, int lane) {
+    for (int c = lane; c < rank; c += 32) qs[c] = ldf(q_lat + c) * scale;
+    const int half = rope_dims / 2;
+    for (int i = lane; i < half; i += 32) {
+        float a, b;
+        rotate_pair(ldf(q_rot + 2 * i), ldf(q_rot + 2 * i + 1), cs[i], cs[half + i], a, b);
+        qs[rank + 2 * i] = a * scale;
+        qs[rank + 2 * i + 1] = b * scale;
+    }
+    for (int c = rope_dims + lane; c < rot_dim; c += 32) qs[rank + c] = ldf(q_rot + c) * scale;
+}
+
+// OACC = ceil(rank / 32): output accumulators per lane.
+template <typename T, int OACC>
+__global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(
+    const T* __restrict__ q_lat,        // [H, total_q, rank]
+    const T* __restrict__ q_raw,        // [total_q, H, q_head_stride]; the rotated part starts at q_rot_off of each head
+    int q_head_stride, int q_rot_off,
+    const T* __restrict__ cache,        // [slots, rank + rot_dim]
+    const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
+    const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
+    const float* __restrict__ sink,     // [H]
+    const float* __restrict__ cos_sin, int rope_dims,
+    T* __restrict__ out,                // [H, total_q, rank]
+    int total_q, int H, int rank, int rot_dim, float scale) {
+    B200_PDL_SYNC();
+    extern __shared__ float smem[];
+    const int D = rank + rot_dim;
+    const int DS = D | 1;                                  // odd row stride: lanes reading one column of 32 rows hit 32 banks
+    float* tile = smem;                                    // [LA_TILE][DS]
+    float* qs = tile + LA_TILE * DS;                       // [LA_WARPS][D]
+    float* pb = qs + LA_WARPS * D;                         // [LA_WARPS][LA_TILE]
+    const int s = blockIdx.y;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair0 = blockIdx.x * LA_WARPS;
+    if (pair0 >= sp.qlen * H) return;
+    const int pair = pair0 + warp;
+    const bool active = pair < sp.qlen * H;
+    const int i = active ? pair / H : 0, h = active ? pair % H : 0;
+    const int first = sp.klen - sp.qlen;                   // position of this step's first token
+    const int pos = first + i;
+    const int i_hi = min(sp.qlen - 1, (pair0 + LA_WARPS - 1) / H);
+    const int kmax = first + i_hi + 1;                     // keys any warp of this CTA may see
+    float* myq = qs + warp * D;
+    if (active) {
+        const int64_t row = sp.q0 + i;
+        load_query(myq, q_lat + ((int64_t)h * total_q + row) * rank, q_raw + (row * H + h) * q_head_stride + q_rot_off,
+                   cos_sin + (int64_t)pos * rope_dims, rank, rot_dim, rope_dims, scale, lane);
+    }
+    float m = active ? sink[h] : 0.f, l = 1.0f;            // the sink: score sink[h], weight exp(0) = 1, no value
+    float acc[OACC];
+#pragma unroll
+    for (int k = 0; k < OACC; ++k) acc[k] = 0.f;
+    const int32_t* bt = block_tables + (int64_t)s * bt_stride;
+    for (int j0 = 0; j0 < kmax; j0 += LA_TILE) {
+        __syncthreads();                                   // previous tile consumed (and the queries written)
+        const int rows = min(LA_TILE, kmax - j0);
+        for (int e = threadIdx.x; e < rows * D; e += blockDim.x) {
+            const int r = e / D, c = e - r * D;
+            const int j = j0 + r;
+            const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
+            tile[r * DS + c] = ldf(cache + slot * D + c);
+        }
+        __syncthreads();
+        if (active && j0 <= pos) {
+            const bool valid = lane < rows && j0 + lane <= pos;
+            float sc = -INFINITY;
+            if (valid) {
+                const float* kr = tile + lane * DS;
+                float a = 0.f;
+                for (int c = 0; c < D; ++c) a = fmaf(myq[c], kr[c], a);
+                sc = a;
+            }
+            const float m_new = fmaxf(m, warp_max(sc));
+            const float alpha = expf(m - m_new);
+            const float p = valid ? expf(sc - m_new) : 0.f;
+            l = l * alpha + warp_sum(p);
+            m = m_new;
+            pb[warp * LA_TILE + lane] = p;
+            __syncwarp();
+            const int nk = min(rows, pos - j0 + 1);
+#pragma unroll
+            for (int k = 0; k < OACC; ++k) {
+                const int c = lane + 32 * k;
+                float a = acc[k] * alpha;
+                if (c < rank)
+                    for (int j = 0; j < nk; ++j) a = fmaf(pb[warp * LA_TILE + j], tile[j * DS + c], a);
+                acc[k] = a;
+            }
+            __syncwarp();
+        }
+    }
+    if (active) {
+        const float inv = 1.0f / l;
+        T* o = out + ((int64_t)h * total_q + sp.q0 + i) * rank;
+#pragma unroll
+        for (int k = 0; k < OACC; ++k) {
+            const int c = lane + 32 * k;
+            if (c < rank) stf(o + c, acc[k] * inv);
+        }
+    }
+}
+
+template <typename K>
+int ensure_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return B200_OK;
+    if (bytes > 227 * 1024) return B200_EUNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        b200_tls_cuda_error() = cudaGetErrorString(e);
+        return B200_ECUDA;
+    }
+    return B200_OK;
+}
+
+template <typename T, int OACC>
+int launch_attn(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
+                const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
+                int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, cudaStream_t stream) {
+    const int D = rank + rot_dim;
+    const size_t smem = sizeof(float) * ((size_t)LA_TILE * (D | 1) + (size_t)LA_WARPS * D + LA_WARPS * LA_TILE);
+    int rc = ensure_smem(latent_attn_kernel<T, OACC>, smem);
+    if (rc != B200_OK) return rc;
+    dim3 grid((max_q * H + LA_WARPS - 1) / LA_WARPS, num_seqs);
+    B200_LAUNCH((latent_attn_kernel<T, OACC>), grid, LA_WARPS * 32, smem, stream, static_cast<const T*>(q_lat),
+                static_cast<const T*>(q_raw), q_head_stride, q_rot_off, static_cast<const T*>(cache), block_tables, bt_stride,
+                block_size, cu_q, cu_k, ctx_lens, sink, cos_sin, rope_dims, static_cast<T*>(out), total_q, H, rank, rot_dim,
+                scale);
+    return b200_launch_status(nullptr);
+}
+
+}  // namespace
+
+extern "C" int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, const float* cos_sin, int rope_dims,
+                                  const int64_t* positions, const int32_t* slots, void* cache, int n, int rank, int rot_dim,
+                                  float eps, int is32, void* stream) {
+    if (!dkv || !norm_w || !cos_sin || !positions || !slots || !cache || n < 0 || rank <= 0 || rot_dim < 0) return B200_EINVAL;
+    if (rope_dims < 0 || rope_dims > rot_dim || (rope_dims & 1)) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    B200M_DISPATCH(is32, B200_LAUNCH((latent_store_kernel<T>), n, 128, 0, static_cast<cudaStream_t>(stream),
+                                     static_cast<const T*>(dkv), stride, static_cast<const T*>(norm_w), cos_sin, rope_dims,
+                                     positions, slots, static_cast<T*>(cache), rank, rot_dim, eps));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                                      const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
+                                      const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
+                                      int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
+                                      int rot_dim, float scale, int is32, void* stream) {
+    if (!q_lat || !q_raw || !cache || !block_tables || !sink || !cos_sin || !out) return B200_EINVAL;
+    if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
+    if (total_q < 0 || num_seqs < 0 || num_heads <= 0 || rank <= 0 || rot_dim < 0 || block_size <= 0) return B200_EINVAL;
+    if (rope_dims < 0 || rope_dims > rot_dim || (rope_dims & 1)) return B200_EINVAL;
+    if (rank > 512) return B200_EUNSUPPORTED;
+    if (total_q == 0 || num_seqs == 0 || max_q <= 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LA_GO(N)                                                                                                              \
+    B200M_DISPATCH(is32, return (launch_attn<T, N>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride,     \
+                                                   block_size, cu_q, cu_k, ctx_lens, sink, cos_sin, rope_dims, out, total_q,  \
+                                                   num_seqs, max_q, num_heads, rank, rot_dim, scale, st)))
+    if (rank <= 128) LA_GO(4);
+    if (rank <= 256) LA_GO(8);
+    LA_GO(16);
+#undef LA_GO
+    return B200_EINVAL;
+}

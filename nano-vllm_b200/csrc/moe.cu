@@ -1,0 +1,209 @@
+// Routed experts: sigmoid router with top-k selection, token -> expert grouping on the device (no host round trip, so a
+// step stays graph-capturable), grouped expert GEMMs over the grouped rows, and the weighted combine.
+//
+//   moe_route_kernel  : scores = sigmoid(logits) in fp32; the `top` largest per token with their scores as weights
+//   moe_align_kernel  : counting sort of the (token, choice) pairs by expert; every expert's run is padded to a multiple of
+//                       the GEMM's row tile so one tile never spans two experts
+//   moe_gemm_kernel   : C[i, :] = act(A[src(i), :] * scale(i)) . W[e(i)]^T, one expert per row tile
+//   moe_combine_kernel: per token, the sum of its choices' rows (fixed order) plus the gated shared expert
+#include "mix_common.cuh"
+
+namespace {
+
+template <int DUMMY>
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top, int32_t* __restrict__ idx,
+                                 float* __restrict__ wgt) {
+    B200_PDL_SYNC();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const float* z = logits + (int64_t)t * ld;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            const float v = z[e];
+            bool taken = false;
+            for (int p = 0; p < k; ++p) taken |= (idx[(int64_t)t * top + p] == e);
+            if (!taken && (best < 0 || v > bv)) {
+                best = e;
+                bv = v;
+            }
+        }
+        idx[(int64_t)t * top + k] = best;
+        wgt[(int64_t)t * top + k] = sigmoidf_(bv);
+    }
+}
+
+// One CTA.  pairs = n * top entries of idx.  Outputs: sorted_rows[cap] (pair index, or -1 for padding), pos_of[pairs]
+// (where each pair went), tile_expert[max_tiles], num_tiles[0].  counts: scratch of 2 * E ints.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restrict__ idx, int pairs, int E, int bm,
+                                                         int32_t* __restrict__ sorted_rows, int cap, int32_t* __restrict__ pos_of,
+                                                         int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles,
+                                                         int32_t* __restrict__ counts) {
+    B200_PDL_SYNC();
+    int32_t* cnt = counts;           // [E] pairs per expert
+    int32_t* start = counts + E;     // [E] first sorted row of the expert
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_rows[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = at;
+            const int tiles = (cnt[e] + bm - 1) / bm;
+            for (int k = 0; k < tiles; ++k) tile_expert[at / bm + k] = e;
+            at += tiles * bm;
+            cnt[e] = 0;
+        }
+        num_tiles[0] = at / bm;
+    }
+    __syncthreads();
+    // rows of one expert in ascending pair order would need a stable sort; the order inside an expert changes nothing in
+    // the results (rows are independent), so an atomic cursor is enough
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = idx[i];
+        const int p = start[e] + atomicAdd(&cnt[e], 1);
+        sorted_rows[p] = i;
+        pos_of[i] = p;
+    }
+}
+
+constexpr int MG_BM = 32, MG_BN = 64, MG_BK = 32;
+
+// A rows: src_rows == nullptr -> row i of A itself (the grouped intermediate); else pair = sorted_rows[i], token = pair / top,
+// A row = tokens[token] * wgt[pair] (rounded to T: it is the expert's input tensor).  act: 0 none, 1 relu^2.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, int64_t a_stride, const int32_t* __restrict__ sorted_rows,
+                                                       const float* __restrict__ wgt, int top, bool gather,
+                                                       const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles,
+                                                       const T* __restrict__ W, int N, int K, TO* __restrict__ C, int act) {
+    B200_PDL_SYNC();
+    const int tile = blockIdx.y;
+    if (tile >= num_tiles[0]) return;
+    __shared__ float As[MG_BM][MG_BK + 1];
+    __shared__ float Ws[MG_BN][MG_BK + 1];
+    __shared__ int src[MG_BM];
+    __shared__ float sc[MG_BM];
+    const int e = tile_expert[tile];
+    const T* We = W + (int64_t)e * N * K;
+    const int row0 = tile * MG_BM, col0 = blockIdx.x * MG_BN;
+    if (threadIdx.x < MG_BM) {
+        const int p = sorted_rows[row0 + threadIdx.x];
+        src[threadIdx.x] = p < 0 ? -1 : (gather ? p / top : row0 + (int)threadIdx.x);
+        sc[threadIdx.x] = (p >= 0 && gather) ? wgt[p] : 1.0f;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 2 rows x 4 columns each
+    float acc[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += MG_BK) {
+        for (int i = threadIdx.x; i < MG_BM * MG_BK; i += 256) {
+            const int r = i / MG_BK, k = i % MG_BK;
+            float v = 0.f;
+            if (src[r] >= 0 && k0 + k < K) {
+                v = ldf(A + (int64_t)src[r] * a_stride + k0 + k);
+                if (gather) v = rnd<T>(v * sc[r]);
+            }
+            As[r][k] = v;
+        }
+        for (int i = threadIdx.x; i < MG_BN * MG_BK; i += 256) {
+            const int c = i / MG_BK, k = i % MG_BK;
+            Ws[c][k] = (col0 + c < N && k0 + k < K) ? ldf(We + (int64_t)(col0 + c) * K + k0 + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < MG_BK; ++k) {
+            const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float w = Ws[tx + 16 * j][k];
+                acc[0][j] = fmaf(a0, w, acc[0][j]);
+                acc[1][j] = fmaf(a1, w, acc[1][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = ty * 2 + r;
+        if (src[row] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = col0 + tx + 16 * j;
+            if (col >= N) continue;
+            float v = acc[r][j];
+            if (act == 1) {
+                v = fmaxf(v, 0.f);
+                v = v * v;
+            }
+            stf(C + (int64_t)(row0 + row) * N + col, v);
+        }
+    }
+}
+
+// out[t, :] = sum_k rows[pos_of[t * top + k], :] + sigmoid(gate_logit[t]) * shared[t, :]
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ pos_of, int top,
+                                   const T* __restrict__ shared, const float* __restrict__ gate_logit, int64_t gate_ld,
+                                   float* __restrict__ out, int n, int width) {
+    B200_PDL_SYNC();
+    const int t = blockIdx.x;
+    float g = 0.f;
+    if (shared) g = gate_logit ? sigmoidf_(gate_logit[(int64_t)t * gate_ld]) : 1.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float a = 0.f;
+        for (int k = 0; k < top; ++k) a += rows[(int64_t)pos_of[(int64_t)t * top + k] * width + c];
+        if (shared) a = fmaf(g, ldf(shared + (int64_t)t * width + c), a);
+        out[(int64_t)t * width + c] = a;
+    }
+}
+
+}  // namespace
+
+extern "C" int b200m_moe_tile_rows(void) { return MG_BM; }
+
+extern "C" int b200m_moe_route(const float* logits, int64_t ld, int n, int num_experts, int top, int32_t* idx, float* wgt, void* stream) {
+    if (!logits || !idx || !wgt || n < 0 || num_experts <= 0 || top <= 0 || top > num_experts) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    B200_LAUNCH((moe_route_kernel<0>), (n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream), logits, ld, n, num_experts, top, idx, wgt);
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_moe_align(const int32_t* idx, int pairs, int num_experts, int32_t* sorted_rows, int cap, int32_t* pos_of,
+                               int32_t* tile_expert, int32_t* num_tiles, int32_t* counts, void* stream) {
+    if (!idx || !sorted_rows || !pos_of || !tile_expert || !num_tiles || !counts || pairs < 0 || num_experts <= 0) return B200_EINVAL;
+    if (cap % MG_BM || cap < ((pairs + num_experts * (MG_BM - 1)) / MG_BM) * MG_BM) return B200_EWORKSPACE;
+    B200_LAUNCH((moe_align_kernel), 1, 1024, 0, static_cast<cudaStream_t>(stream), idx, pairs, num_experts, (int)MG_BM, sorted_rows, cap,
+                pos_of, tile_expert, num_tiles, counts);
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* sorted_rows, const float* wgt, int top, int gather,
+                              const int32_t* tile_expert, const int32_t* num_tiles, int max_tiles, const void* W, int N, int K,
+                              void* C, int out_f32, int act, int is32, void* stream) {
+    if (!A || !sorted_rows || !tile_expert || !num_tiles || !W || !C || N <= 0 || K <= 0 || max_tiles < 0) return B200_EINVAL;
+    if (gather && (!wgt || top <= 0)) return B200_EINVAL;
+    if (max_tiles == 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+    if (out_f32) {
+        B200M_DISPATCH(is32, B200_LAUNCH((moe_gemm_kernel<T, float>), grid, 256, 0, st, static_cast<const T*>(A), a_stride, sorted_rows,
+                                         wgt, top, gather != 0, tile_expert, num_tiles, static_cast<const T*>(W), N, K,
+                                         static_cast<float*>(C), act));
+    } else {
+        B200M_DISPATCH(is32, B200_LAUNCH((moe_gemm_kernel<T, T>), grid, 256, 0, st, static_cast<const T*>(A), a_stride, sorted_rows,
+                                         wgt, top, gather != 0, tile_expert, num_tiles, static_cast<const T*>(W), N, K,
+                                         static_cast<T*>(C), act));
+    }
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_moe_combine(const float* rows, const int32_t* pos_of, int top, const void* shared, const float* gate_logit,
+                                 int64_t gate_ld, float* out, int n, int width, int is32, void* stream) {
+    if (!rows || !pos_of || !out || n < 0 || width <= 0 || top <= 0) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    B200M_DISPATCH(is32, B200_LAUNCH((moe_combine_kernel<T>), n, 256, 0, static_cast<cudaStream_t>(stream), rows, pos_of, top,
+                                     static_cast<const T*>(shared), gate_logit, gate_ld, out, n, width));
+    return b200_launch_status(nullptr);
+}

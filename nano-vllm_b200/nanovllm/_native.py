@@ -45,7 +45,29 @@ SIGNATURES = {
     "b200_layer_tail": (_i, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _vp, _sz, _i, _i, _i, _i, _f, _i, _i, _vp]),
 }
 
+# libb200mix.so (include/b200_mixers.h): mixers of hybrid decoders and their row-wise ops
+_f32p = _vp
+MIX_SIGNATURES = {
+    "b200m_abi_version": (_i, []),
+    "b200m_embed": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
+    "b200m_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200m_rmsnorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _f, _i, _vp]),
+    "b200m_ff_act": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp]),
+    "b200m_latent_store": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "b200m_latent_attention": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                    _f, _i, _vp]),
+    "b200m_causal_conv": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200m_selective_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                  _vp]),
+    "b200m_moe_tile_rows": (_i, []),
+    "b200m_moe_route": (_i, [_vp, _i64, _i, _i, _i, _vp, _vp, _vp]),
+    "b200m_moe_align": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200m_moe_gemm": (_i, [_vp, _i64, _vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _i, _i, _i, _vp]),
+    "b200m_moe_combine": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
+}
+
 _lib = None
+_mix = None
 
 
 class B200Error(RuntimeError):
@@ -73,6 +95,47 @@ def load():
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+def mix_lib_path() -> Path:
+    return Path(os.environ.get("B200MIX_LIB", _LIB_PATH.with_name("libb200mix.so")))
+
+
+def _make(target: str) -> None:
+    """Build one library in-tree (a source checkout without built files): `make -C csrc <target>`."""
+    import subprocess
+    csrc = _LIB_PATH.parent.parent / "csrc"
+    r = subprocess.run(["make", "-C", str(csrc), "-j8", target], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise B200Error(f"building {target} failed:\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}")
+
+
+def load_mix():
+    """dlopen libb200mix.so (built on first use when the checkout has no built library) and type its symbols."""
+    global _mix
+    if _mix is not None:
+        return _mix
+    path = mix_lib_path()
+    if not path.exists():
+        if "B200MIX_LIB" in os.environ:
+            raise B200Error(f"{path} not found")
+        _make("mix")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in MIX_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _mix = lib
+    return lib
+
+
+_CODES = {0: "ok", -1: "invalid argument", -2: "unsupported shape", -3: "CUDA runtime error", -4: "cache not bound",
+          -5: "workspace too small", -6: "device is not compute capability 10.x"}
+
+
+def check_mix(code: int):
+    if code != 0:
+        raise B200Error(f"libb200mix: {_CODES.get(code, 'unknown error')} (code {code})")
 
 
 def check(code: int, ctx=None):

@@ -24,6 +24,10 @@ class Config:
     eos: int = -1
     kvcache_block_size: int = 256
     num_kvcache_blocks: int = -1
+    num_state_slots: int = 0            # set by the runner: recurrent-state slots (0 = the model keeps no per-sequence state)
+    prefix_cache: bool = True           # set by the runner: False for models that cannot skip a cached prefix
+    logits_only: bool = False           # replay mode: steps return logits (ModelRunner.run_logits), nothing is sampled
+    dtype: str = "bfloat16"             # "float32": every tensor in 32 bits, for the models that have such a path
 
     def __post_init__(self):
         bs = self.kvcache_block_size
@@ -34,6 +38,8 @@ class Config:
         if self.hf_config is None:
             if not os.path.isdir(self.model):
                 raise FileNotFoundError(f"model directory not found: {self.model}")
-            from transformers import AutoConfig
-            self.hf_config = AutoConfig.from_pretrained(self.model)
+            from .models.registry import read_config
+            self.hf_config = read_config(self.model)
+        if self.dtype not in ("bfloat16", "float32"):
+            raise ValueError("dtype must be bfloat16 or float32")
         self.max_model_len = min(self.max_model_len, self.hf_config.max_position_embeddings)

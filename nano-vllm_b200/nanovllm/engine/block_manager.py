@@ -46,9 +46,15 @@ class _BlockView:
 
 
 class BlockManager:
-    def __init__(self, num_blocks: int, block_size: int):
+    def __init__(self, num_blocks: int, block_size: int, num_state_slots: int = 0, prefix_cache: bool = True):
+        """``num_state_slots`` > 0: every admitted sequence also takes one recurrent-state slot (lowest free index first)
+        and returns it with its blocks.  ``prefix_cache=False``: no block is ever shared or revived (models whose state at the
+        end of a prefix is not kept cannot skip it)."""
         self.block_size = block_size
         self.num_blocks = num_blocks
+        self.prefix_cache = prefix_cache
+        self.num_state_slots = num_state_slots
+        self.free_state_slots: list[int] = list(range(num_state_slots))
         self._ref = [0] * num_blocks
         self._hash = [-1] * num_blocks
         self._tokens: list[tuple | None] = [None] * num_blocks
@@ -89,7 +95,9 @@ class BlockManager:
         need = nblocks
         hits = 0
         h = -1
-        for i in range(nblocks - 1):
+        if self.num_state_slots and not self.free_state_slots:
+            return -1
+        for i in range(nblocks - 1 if self.prefix_cache else 0):
             toks = seq.block(i)
             h = self.compute_hash(toks, h)
             bid = self.hash_to_block_id.get(h, -1)
@@ -117,6 +125,9 @@ class BlockManager:
         for _ in range(num_cached_blocks, seq.num_blocks):
             table.append(self._take_free_block())
         seq.num_cached_tokens = num_cached_blocks * self.block_size
+        if self.num_state_slots:
+            self.free_state_slots.sort()
+            seq.state_slot = self.free_state_slots.pop(0)
 
     def deallocate(self, seq: Sequence) -> None:
         for bid in reversed(seq.block_table):
@@ -125,6 +136,24 @@ class BlockManager:
                 self._release_block(bid)
         seq.num_cached_tokens = 0
         seq.block_table.clear()
+        if seq.state_slot >= 0:
+            self.free_state_slots.append(seq.state_slot)
+            seq.state_slot = -1
+
+    # ---- growth of a sequence whose tokens arrive in portions (replay) ---------------------------------
+    def can_extend(self, seq: Sequence) -> bool:
+        """Room for the blocks that seq's current token count needs beyond its table (and a state slot at admission)."""
+        if self.num_state_slots and seq.state_slot < 0 and not self.free_state_slots:
+            return False
+        return len(self.free_block_ids) >= seq.num_blocks - len(seq.block_table)
+
+    def extend(self, seq: Sequence) -> None:
+        """Grow seq's block table to cover all of its tokens; the first call admits it (state slot)."""
+        if self.num_state_slots and seq.state_slot < 0:
+            self.free_state_slots.sort()
+            seq.state_slot = self.free_state_slots.pop(0)
+        while len(seq.block_table) < seq.num_blocks:
+            seq.block_table.append(self._take_free_block())
 
     # ---- decode growth -----------------------------------------------------------------------
     def can_append(self, seq: Sequence) -> bool:
@@ -136,6 +165,8 @@ class BlockManager:
 
     # ---- publishing finished blocks to the prefix cache --------------------------------------------
     def hash_blocks(self, seq: Sequence) -> None:
+        if not self.prefix_cache:
+            return
         bs = self.block_size
         first = seq.num_cached_tokens // bs
         last = (seq.num_cached_tokens + seq.num_scheduled_tokens) // bs

@@ -76,15 +76,29 @@ class LLMEngine:
                         os.environ.pop(k, None)
                     else:
                         os.environ[k] = v
-        from transformers import AutoTokenizer
-        self.tokenizer = AutoTokenizer.from_pretrained(config.model, use_fast=True)
-        config.eos = self.tokenizer.eos_token_id if self.tokenizer.eos_token_id is not None else -1
+        self.tokenizer = self._load_tokenizer(config)
+        if self.tokenizer is not None:
+            config.eos = self.tokenizer.eos_token_id if self.tokenizer.eos_token_id is not None else -1
+        else:
+            eos = getattr(config.hf_config, "eos_token_id", None)
+            config.eos = eos if isinstance(eos, int) else -1
         self.scheduler = Scheduler(config)            # after the runner: it needs num_kvcache_blocks
         self._closed = False
         # step-loop accounting (seconds): total wall time of the loop, and the part of it spent blocked on the GPU;
         # total - wait is the host's own work (scheduling, metadata staging, launches, detokenisation)
         self.loop_stats = {"steps": 0, "total_s": 0.0, "wait_s": 0.0}
         atexit.register(self.exit)
+
+    @staticmethod
+    def _load_tokenizer(config):
+        """The checkpoint's tokenizer, or None for a checkpoint that ships none (prompts are then lists of token ids and
+        outputs carry an empty ``text``)."""
+        import os
+        names = ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "vocab.json")
+        if os.path.isdir(config.model) and not any(os.path.exists(os.path.join(config.model, n)) for n in names):
+            return None
+        from transformers import AutoTokenizer
+        return AutoTokenizer.from_pretrained(config.model, use_fast=True)
 
     # ---- rank-0 -> mirror ranks control channel (spawn mode only) --------------------------
     def _tell(self, *cmd):
@@ -124,7 +138,7 @@ class LLMEngine:
 
     def add_request(self, prompt: str | list[int], sampling_params: SamplingParams):
         if isinstance(prompt, str):
-            prompt = self.tokenizer.encode(prompt)
+            prompt = self._encode(prompt)
         self._tell("add", prompt, sampling_params)
         self._add_request(prompt, sampling_params)
 
@@ -138,6 +152,11 @@ class LLMEngine:
         if lo < 0 or hi >= vocab:
             raise ValueError(f"prompt token id {lo if lo < 0 else hi} is outside the vocabulary [0, {vocab})")
         self.scheduler.add(Sequence(prompt, sampling_params))
+
+    def _encode(self, text: str) -> list[int]:
+        if self.tokenizer is None:
+            raise ValueError("this checkpoint has no tokenizer: pass prompts as lists of token ids")
+        return self.tokenizer.encode(text)
 
     def step(self):
         self._tell("step")
@@ -156,7 +175,7 @@ class LLMEngine:
 
     def generate(self, prompts: list[str] | list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
                  use_tqdm: bool = True) -> list[dict]:
-        prompts = [self.tokenizer.encode(p) if isinstance(p, str) else list(p) for p in prompts]
+        prompts = [self._encode(p) if isinstance(p, str) else list(p) for p in prompts]
         self._tell("generate", prompts, sampling_params)
         return self._generate(prompts, sampling_params, use_tqdm and self.rank == 0)
 
@@ -179,7 +198,7 @@ class LLMEngine:
                 stats["decode"] = -num_tokens / dt
             for seq in finished:                  # detokenise now: the next step is already running on the GPU
                 toks = seq.completion_token_ids
-                done[seq.seq_id] = {"text": self.tokenizer.decode(toks), "token_ids": toks}
+                done[seq.seq_id] = {"text": self.tokenizer.decode(toks) if self.tokenizer is not None else "", "token_ids": toks}
             if pbar is not None:
                 pbar.set_postfix({"Prefill": f"{int(stats['prefill'])}tok/s", "Decode": f"{int(stats['decode'])}tok/s"})
                 pbar.update(len(finished))

@@ -30,8 +30,8 @@ import torch.distributed as dist
 from .. import _native as nat
 from .. import ops
 from ..config import Config
-from ..models.qwen3 import Qwen3ForCausalLM
-from ..utils.context import reset_context, set_context
+from ..models.registry import model_class
+from ..utils.context import get_context, reset_context, set_context
 from ..utils.loader import load_model
 from .sequence import Sequence
 
@@ -101,7 +101,16 @@ class ModelRunner:
             raise ValueError("CUDA graphs need the NCCL backend (gloo collectives cannot be captured): pass enforce_eager=True")
         if self.world_size > 1:
             assert dist.get_world_size() == self.world_size, "tensor_parallel_size must equal the process-group size"
-        self.native = nat.handle(local)
+        cls = model_class(hf)
+        self.owns_cache = hasattr(cls, "bind_cache")         # the model lays out its own cache / state (hybrid decoders)
+        self.native = None if self.owns_cache else nat.handle(local)
+        self.dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[config.dtype]
+        if self.dtype == torch.float32:
+            if not self.owns_cache:
+                raise ValueError(f"{cls.__name__} has no float32 path")
+            torch.backends.cuda.matmul.allow_tf32 = False    # true 32-bit products
+            torch.backends.cudnn.allow_tf32 = False
+        self.logits_only = bool(getattr(config, "logits_only", False))
         # Sampling randomness: a fresh 63-bit seed per engine unless one is given (B200_SAMPLE_SEED or the argument);
         # every tensor-parallel rank must use the same one (each scores its own vocabulary shard with the RNG keyed by
         # the global token id), so rank 0's choice is broadcast.
@@ -115,7 +124,13 @@ class ModelRunner:
             sample_seed = int(t.item())
         self.sample_seed = sample_seed
 
-        self.model = Qwen3ForCausalLM(hf, rank, self.world_size, self.device, max_position=hf.max_position_embeddings)
+        kw = dict(dtype=self.dtype) if self.owns_cache else {}
+        self.model = cls(hf, rank, self.world_size, self.device, max_position=min(hf.max_position_embeddings, config.max_model_len), **kw) \
+            if self.owns_cache else cls(hf, rank, self.world_size, self.device, max_position=hf.max_position_embeddings)
+        self.needs_block_tables = bool(getattr(self.model, "needs_block_tables", False))
+        self.has_state = bool(getattr(self.model, "has_recurrent_state", False))
+        config.num_state_slots = config.max_num_seqs if self.has_state else 0
+        config.prefix_cache = bool(getattr(self.model, "supports_prefix_cache", True))
         load_model(self.model, config.model, allow_random=bool(os.environ.get("NANOVLLM_ALLOW_RANDOM_INIT")))
         self.vocab_offset = rank * self.model.vocab_shard
         if self.world_size > 1:
@@ -175,17 +190,17 @@ class ModelRunner:
         self.d_off = {}
         mb = self.cap_bs
         for name, count, size in (("step", 1, 8), ("ids", mb, 8), ("pos", mb, 8), ("slot", mb, 4), ("ctx", mb, 4),
-                                  ("temp", mb, 4), ("src", mb, 4), ("bt", mb * W, 4)):
+                                  ("temp", mb, 4), ("src", mb, 4), ("sslot", mb, 4), ("bt", mb * W, 4)):
             self.d_off[name] = o
             o = _align(o + count * size)
         self.d_bytes = o
-        prefill_bytes = _align(8) + 2 * _align(T * 8) + _align(T * 4) + 2 * _align((S + 1) * 4) + _align(S * 4) + _align(S * W * 4)
+        prefill_bytes = _align(8) + 2 * _align(T * 8) + 2 * _align(T * 4) + 2 * _align((S + 1) * 4) + 2 * _align(S * 4) + _align(S * W * 4)
         self.stage = _Staging(self.d_bytes, hosts=2)         # ping-pong: step N+1 is staged while step N runs
         self.pstage = _Staging(prefill_bytes)
         st = self.stage
         spec = (("step", 1, np.int64, torch.int64), ("ids", mb, np.int64, torch.int64), ("pos", mb, np.int64, torch.int64),
                 ("slot", mb, np.int32, torch.int32), ("ctx", mb, np.int32, torch.int32), ("temp", mb, np.float32, torch.float32),
-                ("src", mb, np.int32, torch.int32), ("bt", mb * W, np.int32, torch.int32))
+                ("src", mb, np.int32, torch.int32), ("sslot", mb, np.int32, torch.int32), ("bt", mb * W, np.int32, torch.int32))
         self.hd = [{name: st.host_view(self.d_off[name], cnt, npdt, k) for name, cnt, npdt, _ in spec} for k in range(2)]
         for h in self.hd:
             h["bt"] = h["bt"].reshape(mb, W)
@@ -193,11 +208,17 @@ class ModelRunner:
         g = {name: st.dev_view(self.d_off[name], cnt, npdt, tdt) for name, cnt, npdt, tdt in spec}
         self.g_step, self.g_ids, self.g_pos, self.g_slot = g["step"], g["ids"], g["pos"], g["slot"]
         self.g_ctx, self.g_temp, self.g_bt, self.g_src = g["ctx"], g["temp"], g["bt"].view(mb, W), g["src"]
+        self.g_sslot = g["sslot"]
+        for h in self.hd:
+            h["sslot"][:] = 0
         self.g_bt.zero_()
         self._host_k = 0
         self.g_tokens = torch.zeros(S, dtype=torch.int64, device="cuda")
         self.g_keys = torch.zeros(S, dtype=torch.int64, device="cuda")
         self.g_keyws = torch.zeros(S, dtype=torch.int64, device="cuda")      # running-max keys of the fused LM head (zero between steps)
+        # logits-only steps (replaying a recorded schedule): decode graphs leave their fp32 logits here
+        self.g_logits = torch.zeros(S, self.config.hf_config.vocab_size, dtype=torch.float32, device="cuda") if self.logits_only else None
+        self._last_logits = None
         self.fused_lm_head = os.environ.get("B200_LM_HEAD", "gemm") == "fused"
         self.h_tokens = [torch.empty(S, dtype=torch.int64, pin_memory=True) for _ in range(2)]
         self.h_err = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]   # peer-exchange error flag per step
@@ -219,11 +240,22 @@ class ModelRunner:
         seqs = [Sequence([0] * seq_len) for _ in range(num_seqs)]
         for s in seqs:
             s.num_scheduled_tokens = seq_len
+        if self.owns_cache:
+            # such a model has no cache-less path: lend it a cache of exactly the warm-up's size, pages in order
+            per = -(-seq_len // self.block_size)
+            self.model.bind_cache(per * num_seqs, self.block_size, num_seqs)
+            for i, s in enumerate(seqs):
+                s.block_table = list(range(i * per, (i + 1) * per))
+                s.state_slot = i
         self.run(seqs, True)
+        if self.owns_cache:
+            self.model.unbind_cache()
         torch.cuda.empty_cache()
 
     def kv_block_bytes(self) -> int:
         hf = self.config.hf_config
+        if self.owns_cache:
+            return max(self.model.cache_block_bytes(self.block_size), 1)
         return 2 * hf.num_hidden_layers * self.block_size * self.model.num_kv_heads * self.model.head_dim * 2
 
     def allocate_kv_cache(self):
@@ -236,7 +268,10 @@ class ModelRunner:
             used = total - free
             stats = torch.cuda.memory_stats()
             peak, current = stats["allocated_bytes.all.peak"], stats["allocated_bytes.all.current"]
-            nblk = int(total * cfg.gpu_memory_utilization - used - peak + current) // self.kv_block_bytes()
+            state_bytes = self.model.state_slot_bytes() * cfg.num_state_slots if self.owns_cache else 0
+            nblk = int(total * cfg.gpu_memory_utilization - used - peak + current - state_bytes) // self.kv_block_bytes()
+            if self.owns_cache:                          # no sequence is longer than max_model_len: more blocks than that are never used
+                nblk = min(nblk, cfg.max_num_seqs * self.max_blocks)
             if self.world_size > 1:                      # replicas must agree on the block count
                 t = torch.tensor([nblk], dtype=torch.int64, device="cuda")
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -245,6 +280,10 @@ class ModelRunner:
         if cfg.num_kvcache_blocks <= 0:
             raise RuntimeError("not enough GPU memory for a single KV-cache block")
         m = self.model
+        if self.owns_cache:
+            m.bind_cache(cfg.num_kvcache_blocks, self.block_size, cfg.num_state_slots)
+            self.kv_cache = None
+            return
         self.kv_cache = torch.zeros(ops.kv_cache_shape(hf.num_hidden_layers, cfg.num_kvcache_blocks, m.num_kv_heads,
                                                        self.block_size, m.head_dim), dtype=torch.bfloat16, device="cuda")
         ops.bind_kv_cache(self.kv_cache)
@@ -291,8 +330,10 @@ class ModelRunner:
                    cu_seqlens_q=np.asarray(cu_q, dtype=np.int32), cu_seqlens_k=np.asarray(cu_k, dtype=np.int32),
                    max_seqlen_q=max_q, max_seqlen_k=max_k,
                    slot_mapping=np.concatenate(slots) if slots else np.zeros(0, np.int32), block_tables=None)
-        if cu_k[-1] > cu_q[-1]:
+        if cu_k[-1] > cu_q[-1] or (getattr(self, "needs_block_tables", False) and slots):
             out["block_tables"] = self.prepare_block_tables(seqs)
+        if getattr(self, "has_state", False):
+            out["state_slots"] = np.fromiter((s.state_slot for s in seqs), dtype=np.int32, count=len(seqs))
         return out
 
     def decode_arrays(self, seqs: list[Sequence]) -> dict:
@@ -304,10 +345,13 @@ class ModelRunner:
         last_blk = np.fromiter((s.block_table[-1] for s in seqs), dtype=np.int64, count=n)
         # last_block_num_tokens = len - (num_blocks - 1) * bs, so the slot of the newest token is:
         slots = last_blk * bs + (lens - 1) % bs
-        return dict(input_ids=ids, positions=lens - 1, slot_mapping=slots.astype(np.int32),
-                    context_lens=lens.astype(np.int32), block_tables=self.prepare_block_tables(seqs))
+        out = dict(input_ids=ids, positions=lens - 1, slot_mapping=slots.astype(np.int32),
+                   context_lens=lens.astype(np.int32), block_tables=self.prepare_block_tables(seqs))
+        if getattr(self, "has_state", False):
+            out["state_slots"] = np.fromiter((s.state_slot for s in seqs), dtype=np.int32, count=n)
+        return out
 
-    def prepare_prefill(self, seqs: list[Sequence]):
+    def prepare_prefill(self, seqs: list[Sequence], logit_rows=None):
         a = self.prefill_arrays(seqs)
         st = self.pstage
         off = 0
@@ -319,6 +363,10 @@ class ModelRunner:
                 ("temps", np.fromiter((s.temperature for s in seqs), dtype=np.float32, count=len(seqs)), torch.float32)]
         if a["block_tables"] is not None:
             plan.append(("block_tables", np.ascontiguousarray(a["block_tables"]).reshape(-1), torch.int32))
+        if "state_slots" in a:
+            plan.append(("state_slots", a["state_slots"], torch.int32))
+        if logit_rows is not None:
+            plan.append(("logit_rows", np.asarray(logit_rows, dtype=np.int32), torch.int32))
         for name, arr, tdt in plan:
             h, d = st.views(off, arr.size, arr.dtype, tdt)
             h[:] = arr
@@ -331,7 +379,7 @@ class ModelRunner:
             bt = bt.view(len(seqs), -1)
         slot = views["slot_mapping"] if a["slot_mapping"].size else None
         set_context(True, views["cu_seqlens_q"], views["cu_seqlens_k"], a["max_seqlen_q"], a["max_seqlen_k"],
-                    slot, None, bt)
+                    slot, None, bt, views.get("state_slots"), views.get("logit_rows"))
         return views["input_ids"], views["positions"], views["temps"], views["step"]
 
     def _padded_rows(self, n: int) -> int:
@@ -353,6 +401,8 @@ class ModelRunner:
         h["slot"][:n] = a["slot_mapping"]
         h["ctx"][:n] = a["context_lens"]
         h["temp"][:n] = np.fromiter((s.temperature for s in seqs), dtype=np.float32, count=n)
+        if self.has_state:
+            h["sslot"][:n] = a["state_slots"]
         if padded > n:                                       # graph padding rows (model_runner.py:206-208)
             h["ids"][n:padded] = 0
             h["pos"][n:padded] = 0
@@ -384,7 +434,7 @@ class ModelRunner:
         if src is not None:
             ops.gather_tokens(self.g_ids[:n], self.g_src[:n], self.g_tokens)
         set_context(False, slot_mapping=self.g_slot[:padded], context_lens=self.g_ctx[:padded],
-                    block_tables=self.g_bt[:padded])
+                    block_tables=self.g_bt[:padded], state_slots=self.g_sslot[:padded] if self.has_state else None)
 
     # ---- model + sampling -------------------------------------------------------------------------
     def _forward_and_sample(self, input_ids, positions, temps, step_dev, rows: int):
@@ -405,6 +455,13 @@ class ModelRunner:
                 self.g_tokens[:rows].copy_(ops.tokens_from_keys(keys))
             return
         logits = self.model.compute_logits(hidden)
+        if self.logits_only:                                  # replay: the step's result is its logits, nothing is sampled
+            if logits.shape[0] <= self.g_logits.shape[0] and get_context().logit_rows is None and not get_context().is_prefill:
+                self.g_logits[:logits.shape[0]].copy_(logits)          # decode: static buffer (the step may be a graph replay)
+                self._last_logits = self.g_logits[:logits.shape[0]]
+            else:
+                self._last_logits = logits.float()
+            return
         if self.world_size == 1:
             ops.sample(logits, temps, self.sample_seed, 0, out=self.g_tokens[:rows], step_dev=step_dev)
         else:
@@ -419,7 +476,7 @@ class ModelRunner:
         return self.collect()
 
     @torch.inference_mode()
-    def launch(self, seqs: list[Sequence], is_prefill: bool, staged: int | None = None, src=None) -> None:
+    def launch(self, seqs: list[Sequence], is_prefill: bool, staged: int | None = None, src=None, logit_rows=None) -> None:
         """Enqueue one step (metadata upload, forward, sampling, token read-back) without waiting for it.
         Up to two steps may be in flight; collect() returns them in launch order."""
         n = len(seqs)
@@ -427,7 +484,7 @@ class ModelRunner:
         prof = self._prof
         ev0 = None
         if is_prefill:
-            ids, pos, temps, step_dev = self.prepare_prefill(seqs)
+            ids, pos, temps, step_dev = self.prepare_prefill(seqs, logit_rows)
             if prof is not None:
                 ev0 = torch.cuda.Event(enable_timing=True)
                 ev0.record()
@@ -443,6 +500,8 @@ class ModelRunner:
             if padded in self.graphs and not self.enforce_eager and n <= self.max_bs:
                 self.graphs[padded].replay()
                 ops.LAUNCHES[0] += self.graph_kernels[padded]
+                if self.logits_only:
+                    self._last_logits = self.g_logits[:padded]
             else:
                 self._forward_and_sample(self.g_ids[:n], self.g_pos[:n], self.g_temp[:n], self.g_step, n)
         if prof is not None:
@@ -463,6 +522,25 @@ class ModelRunner:
         self._pending.append((kk, n))
         self.d2h_bytes_last = n * 8
         reset_context()
+
+    def run_logits(self, seqs: list[Sequence], is_prefill: bool, rows: list[int] | None = None) -> torch.Tensor:
+        """One step of a logits-only runner (Config.logits_only): the same launch as run(), returning fp32 logits on the
+        host instead of sampled tokens.  Varlen steps: the logits of the step's flat token rows ``rows`` (any number, also
+        none).  Decode steps: one row per sequence, ``rows`` selects among them."""
+        assert self.logits_only, "run_logits needs Config.logits_only"
+        if is_prefill:
+            self.launch(seqs, True, logit_rows=list(rows) if rows else [0])
+        else:
+            self.launch(seqs, False)
+        self.collect()
+        out = self._last_logits
+        if not is_prefill:
+            out = out[:len(seqs)]
+            if rows is not None:
+                out = out[list(rows)] if rows else out[:0]
+        elif not rows:
+            out = out[:0]
+        return out.float().cpu()
 
     def collect(self) -> list[int]:
         """Wait for the oldest step enqueued by launch() (that step's only host sync) and return its token ids."""
@@ -497,7 +575,8 @@ class ModelRunner:
         self.stage.upload(self.d_bytes, 0)
         torch.cuda.synchronize()
         for bs in reversed(self.graph_bs):
-            set_context(False, slot_mapping=self.g_slot[:bs], context_lens=self.g_ctx[:bs], block_tables=self.g_bt[:bs])
+            set_context(False, slot_mapping=self.g_slot[:bs], context_lens=self.g_ctx[:bs], block_tables=self.g_bt[:bs],
+                        state_slots=self.g_sslot[:bs] if self.has_state else None)
             args = (self.g_ids[:bs], self.g_pos[:bs], self.g_temp[:bs], self.g_step, bs)
             self._forward_and_sample(*args)                  # warm-up outside capture
             torch.cuda.synchronize()

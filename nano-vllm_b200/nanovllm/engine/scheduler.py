@@ -25,7 +25,10 @@ class Scheduler:
         self.max_num_batched_tokens = config.max_num_batched_tokens
         self.eos = config.eos
         self.block_size = config.kvcache_block_size
-        self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size)
+        # a model with per-sequence recurrent state gets one state slot per sequence that may be live, and no prefix cache
+        self.block_manager = BlockManager(config.num_kvcache_blocks, config.kvcache_block_size,
+                                          num_state_slots=getattr(config, "num_state_slots", 0),
+                                          prefix_cache=getattr(config, "prefix_cache", True))
         self.waiting: deque[Sequence] = deque()
         self.running: deque[Sequence] = deque()
 
@@ -112,6 +115,49 @@ class Scheduler:
                 seq.status = SequenceStatus.FINISHED
                 bm.deallocate(seq)
                 self.running.remove(seq)
+
+    # ---- replaying a recorded schedule -------------------------------------------------------------------
+    def plan_step(self, portions: list[tuple[Sequence, list[int]]]) -> tuple[list[Sequence], bool]:
+        """One step whose content is dictated from outside: every (sequence, next tokens) pair runs in this step, prompt
+        portions beside single tokens.  Admits new sequences (blocks, state slot), grows the others, and returns the batch
+        in the form ``schedule()`` returns it: a decode step when every sequence brings exactly one token on top of cached
+        ones, a varlen step otherwise.  ``postprocess_replay`` closes the step; ``retire`` ends a sequence."""
+        bm = self.block_manager
+        batch = []
+        for seq, tokens in portions:
+            if not tokens:
+                raise ValueError("a portion needs at least one token")
+            if seq.status is SequenceStatus.WAITING and not seq.block_table and seq.num_cached_tokens == 0 and seq.num_tokens == len(tokens):
+                pass                                   # first portion: the sequence was created with exactly these tokens
+            else:
+                seq.extend_tokens(tokens)
+            if not bm.can_extend(seq):
+                raise RuntimeError("out of cache blocks or state slots for the dictated step")
+            bm.extend(seq)
+            if seq not in self.running:
+                if len(self.running) >= self.max_num_seqs:
+                    raise RuntimeError("more live sequences than max_num_seqs")
+                seq.status = SequenceStatus.RUNNING
+                self.running.append(seq)
+            seq.num_scheduled_tokens = len(tokens)
+            batch.append(seq)
+        if sum(s.num_scheduled_tokens for s in batch) > self.max_num_batched_tokens:
+            raise RuntimeError("the dictated step exceeds max_num_batched_tokens")
+        decode = all(s.num_scheduled_tokens == 1 and s.num_cached_tokens > 0 for s in batch)
+        for s in batch:
+            s.is_prefill = not decode
+        return batch, not decode
+
+    def postprocess_replay(self, seqs: list[Sequence]) -> None:
+        for seq in seqs:
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            seq.num_scheduled_tokens = 0
+
+    def retire(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.FINISHED
+        self.block_manager.deallocate(seq)
+        if seq in self.running:
+            self.running.remove(seq)
 
     def abort_all(self) -> list[Sequence]:
         """Retire every queued and running sequence, free its blocks and forget the prefix cache: the state after a

@@ -27,7 +27,7 @@ class Sequence:
 
     __slots__ = ("seq_id", "status", "token_ids", "last_token", "num_tokens", "num_prompt_tokens",
                  "num_cached_tokens", "num_scheduled_tokens", "is_prefill", "block_table",
-                 "temperature", "max_tokens", "ignore_eos")
+                 "temperature", "max_tokens", "ignore_eos", "state_slot")
 
     def __init__(self, token_ids: list[int], sampling_params: SamplingParams = _DEFAULT_SP):
         if not token_ids:
@@ -41,6 +41,7 @@ class Sequence:
         self.num_scheduled_tokens = 0     # tokens the current step computes
         self.is_prefill = True
         self.block_table: list[int] = []
+        self.state_slot = -1              # recurrent-state slot (models with per-sequence state), held like the blocks
         self.temperature = sampling_params.temperature
         self.max_tokens = sampling_params.max_tokens
         self.ignore_eos = sampling_params.ignore_eos
@@ -81,6 +82,12 @@ class Sequence:
         bs = self.block_size
         return self.token_ids[i * bs:(i + 1) * bs]
 
+    def extend_tokens(self, token_ids) -> None:
+        """Append given tokens (replaying a recorded request: its tokens arrive step by step)."""
+        self.token_ids.extend(token_ids)
+        self.last_token = self.token_ids[-1]
+        self.num_tokens = len(self.token_ids)
+
     def append_token(self, token_id: int) -> None:
         self.token_ids.append(token_id)
         self.last_token = token_id
@@ -91,11 +98,12 @@ class Sequence:
     def __getstate__(self):
         tail = self.token_ids if self.is_prefill else self.last_token
         return (self.num_tokens, self.num_prompt_tokens, self.num_cached_tokens,
-                self.num_scheduled_tokens, self.block_table, tail)
+                self.num_scheduled_tokens, self.block_table, tail, self.state_slot)
 
     def __setstate__(self, state):
         (self.num_tokens, self.num_prompt_tokens, self.num_cached_tokens,
-         self.num_scheduled_tokens, self.block_table, tail) = state
+         self.num_scheduled_tokens, self.block_table, tail) = state[:6]
+        self.state_slot = state[6] if len(state) > 6 else -1
         if isinstance(tail, list):
             self.token_ids, self.last_token, self.is_prefill = tail, tail[-1], True
         else:

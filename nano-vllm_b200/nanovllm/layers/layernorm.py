@@ -21,3 +21,17 @@ class RMSNorm(nn.Module):
         if residual is None:
             return ops.rmsnorm(x, self.weight, self.eps)
         return ops.add_rmsnorm(x, residual, self.weight, self.eps)
+
+
+class ResidualLayerNorm:
+    """Weight-only layer norm reading an fp32 residual stream, fused with the stream's update: ``x += a + b`` (the two
+    branches of a parallel block, summed first), then ``(x - mean) / sqrt(var + eps) * w`` in the model's activation type.
+    A plain object (no nn.Module): ``weight`` is a device tensor set by the model's loader."""
+
+    def __init__(self, width: int, eps: float, dtype, device):
+        self.eps = eps
+        self.weight = torch.ones(width, dtype=dtype, device=device)
+
+    def __call__(self, x, a=None, b=None, b32=None, rows_idx=None):
+        from .. import mixops
+        return mixops.add_layernorm(x, self.weight, self.eps, a=a, b=b, b32=b32, rows_idx=rows_idx)

@@ -1,0 +1,248 @@
+"""Tensor-facing wrappers over libb200mix.so (include/b200_mixers.h): the mixers of hybrid decoders and their row-wise
+ops.  Like ``ops``: every function is one launch (``causal_conv``: two) of a hand-written sm_100a kernel on the current
+stream, PyTorch only supplies memory and streams, and there is no CPU path.
+
+Activations, weights and caches are bf16 or fp32 (one type per call, taken from the tensors); residual stream, recurrent
+state, router logits and softmax statistics are fp32 in both.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _native as nat
+from . import ops
+
+
+@dataclass
+class StepSpans:
+    """Which tokens of a step belong to which sequence, in the two forms the kernels take.
+
+    varlen step:  cu_q, cu_k int32 [S + 1] (cumulative tokens of this step / tokens held after it), max_q on the host
+    decode step:  ctx_lens int32 [S] (tokens held after the step, 0 = padding row), one token per row
+    """
+    num_seqs: int
+    max_q: int
+    cu_q: torch.Tensor | None = None
+    cu_k: torch.Tensor | None = None
+    ctx_lens: torch.Tensor | None = None
+
+
+def _is32(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise nat.B200Error("tensors must be on a CUDA device (there is no CPU path)")
+    if t.dtype == torch.float32:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise nat.B200Error(f"unsupported dtype {t.dtype}")
+
+
+def _same(is32: int, *tensors):
+    for t in tensors:
+        if t is not None and _is32(t) != is32:
+            raise nat.B200Error("all tensors of a call must share one dtype")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return ops._stream()          # counts the launch too
+
+
+def _call(name, *args):
+    nat.check_mix(getattr(nat.load_mix(), name)(*args))
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """ids int64 [n] -> fp32 [n, width]."""
+    assert ids.dtype == torch.int64 and ids.is_contiguous() and table.is_contiguous()
+    n, width = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty(n, width, dtype=torch.float32, device=table.device)
+    _call("b200m_embed", ids.data_ptr(), table.data_ptr(), out.data_ptr(), n, width, table.shape[0], _is32(table), _stream())
+    return out
+
+
+def add_layernorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, a=None, b=None, b32=None, rows_idx=None,
+                  out: torch.Tensor | None = None, norm: bool = True):
+    """x (fp32 [rows, cols], updated in place) += a + b + b32; returns the weight-only layer norm of the updated rows
+    (dtype of ``weight``), or None with ``norm=False``.  ``rows_idx``: normalise these rows only, add nothing."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    rows, cols = x.shape
+    for t in (a, b, b32):
+        assert t is None or (t.is_contiguous() and t.shape == x.shape)
+    assert b32 is None or b32.dtype == torch.float32
+    ref = weight if weight is not None else (a if a is not None else b)
+    is32 = _is32(ref) if ref is not None else 1
+    _same(is32, a, b, weight)
+    n_out = rows
+    if rows_idx is not None:
+        assert rows_idx.dtype == torch.int32 and a is None and b is None and b32 is None
+        n_out = rows_idx.numel()
+    if norm and out is None:
+        out = torch.empty(n_out, cols, dtype=weight.dtype, device=x.device)
+    _call("b200m_add_layernorm", x.data_ptr(), _p(a), _p(b), _p(b32), _p(weight), _p(out) if norm else None, _p(rows_idx),
+          n_out, cols, eps, is32, _stream())
+    return out if norm else None
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, cols: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMS norm over the first ``cols`` elements of each row of a 2-D, unit-inner-stride x."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    cols = x.shape[1] if cols is None else cols
+    is32 = _is32(x)
+    _same(is32, weight)
+    if out is None:
+        out = torch.empty(x.shape[0], cols, dtype=x.dtype, device=x.device)
+    _call("b200m_rmsnorm", x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), x.shape[0], cols, eps,
+          is32, _stream())
+    return out
+
+
+FF_GELU_TANH_MUL, FF_RELU2, FF_SILU_MUL = 0, 1, 2
+
+
+def ff_act(x: torch.Tensor, kind: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    assert x.dim() == 2 and x.is_contiguous()
+    n = x.shape[1] if kind == FF_RELU2 else x.shape[1] // 2
+    if out is None:
+        out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+    _call("b200m_ff_act", x.data_ptr(), out.data_ptr(), x.shape[0], n, kind, _is32(x), _stream())
+    return out
+
+
+# ---- latent attention ----------------------------------------------------------------------------------------------------
+def latent_store(dkv: torch.Tensor, norm_w: torch.Tensor, cos_sin: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                 cache: torch.Tensor, rank: int, rot_dim: int, eps: float) -> None:
+    """dkv [n, >= rank + rot_dim] -> cache rows [slots_total, rank + rot_dim] at ``slots`` (int32, -1 = skip)."""
+    assert dkv.dim() == 2 and dkv.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == rank + rot_dim
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    assert positions.dtype == torch.int64 and slots.dtype == torch.int32 and slots.numel() == dkv.shape[0]
+    is32 = _is32(dkv)
+    _same(is32, norm_w, cache)
+    _call("b200m_latent_store", dkv.data_ptr(), dkv.stride(0), norm_w.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1],
+          positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), dkv.shape[0], rank, rot_dim, eps, is32, _stream())
+
+
+def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, cache: torch.Tensor, block_tables: torch.Tensor,
+                     block_size: int, spans: StepSpans, sink: torch.Tensor, cos_sin: torch.Tensor, scale: float,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """q_lat [H, n, rank], q_raw [n, H, head_stride] -> [H, n, rank]."""
+    H, n, rank = q_lat.shape
+    rot_dim = cache.shape[-1] - rank
+    assert q_lat.is_contiguous() and q_raw.is_contiguous() and q_raw.shape[:2] == (n, H) and cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and sink.dtype == torch.float32
+    is32 = _is32(q_lat)
+    _same(is32, q_raw, cache)
+    if out is None:
+        out = torch.empty_like(q_lat)
+    _call("b200m_latent_attention", q_lat.data_ptr(), q_raw.data_ptr(), q_raw.shape[2], q_rot_off, cache.data_ptr(),
+          block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
+          sink.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1], out.data_ptr(), n, spans.num_seqs, spans.max_q, H, rank,
+          rot_dim, scale, is32, _stream())
+    return out
+
+
+# ---- selective scan ------------------------------------------------------------------------------------------------------
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
+                state_slots: torch.Tensor, spans: StepSpans, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [n, channels] (row-strided view) -> silu(conv(x) + bias) [n, channels]; conv_state [slots, taps - 1, channels] fp32
+    is read for the history and left holding the inputs that follow."""
+    channels, taps = weight.shape
+    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[1] == channels and weight.is_contiguous()
+    assert conv_state.dtype == torch.float32 and conv_state.is_contiguous() and state_slots.dtype == torch.int32
+    is32 = _is32(x)
+    _same(is32, weight, bias)
+    if out is None:
+        out = torch.empty(x.shape[0], channels, dtype=x.dtype, device=x.device)
+    _call("b200m_causal_conv", x.data_ptr(), x.stride(0), weight.data_ptr(), _p(bias), conv_state.data_ptr(), state_slots.data_ptr(),
+          _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, spans.max_q, channels, taps, is32,
+          _stream())
+    if taps > 1:
+        ops.LAUNCHES[0] += 1
+    return out
+
+
+def selective_scan(u, dt_raw, dt_bias, A, Bm, Cm, Dv, z, state, state_slots, spans: StepSpans, out=None) -> torch.Tensor:
+    """u, dt_raw [n, C]; Bm, Cm [n, N] and z [n, C] may be column slices of wider rows; A fp32 [C, N]; state fp32 [slots, C, N]."""
+    n, channels = u.shape
+    nstate = A.shape[1]
+    assert u.is_contiguous() and dt_raw.is_contiguous() and A.dtype == torch.float32 and A.is_contiguous()
+    assert Bm.stride(1) == 1 and Cm.stride(1) == 1 and Bm.stride(0) == Cm.stride(0) and z.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (channels, nstate)
+    is32 = _is32(u)
+    _same(is32, dt_raw, dt_bias, Bm, Cm, Dv, z)
+    if out is None:
+        out = torch.empty_like(u)
+    _call("b200m_selective_scan", u.data_ptr(), dt_raw.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
+          Bm.stride(0), Dv.data_ptr(), z.data_ptr(), z.stride(0), state.data_ptr(), state_slots.data_ptr(), _p(spans.cu_q),
+          _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, channels, nstate, is32, _stream())
+    return out
+
+
+# ---- routed experts ------------------------------------------------------------------------------------------------------
+def moe_tile_rows() -> int:
+    return nat.load_mix().b200m_moe_tile_rows()
+
+
+def moe_capacity(pairs: int, num_experts: int) -> int:
+    """Rows of the grouped buffers for `pairs` (token, choice) pairs: every expert's run is padded to a row tile."""
+    bm = moe_tile_rows()
+    return (pairs + num_experts * (bm - 1) + bm - 1) // bm * bm
+
+
+def moe_route(logits: torch.Tensor, num_experts: int, top: int):
+    """logits fp32 [n, >= num_experts] -> (idx int32 [n, top], weights fp32 [n, top])."""
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    n = logits.shape[0]
+    idx = torch.empty(n, top, dtype=torch.int32, device=logits.device)
+    wgt = torch.empty(n, top, dtype=torch.float32, device=logits.device)
+    _call("b200m_moe_route", logits.data_ptr(), logits.stride(0), n, num_experts, top, idx.data_ptr(), wgt.data_ptr(), _stream())
+    return idx, wgt
+
+
+def moe_align(idx: torch.Tensor, num_experts: int):
+    """-> (sorted_rows [cap], pos_of [pairs], tile_expert [cap / tile], num_tiles [1]) int32, all on the device."""
+    pairs = idx.numel()
+    cap = moe_capacity(pairs, num_experts)
+    dev = idx.device
+    sorted_rows = torch.empty(cap, dtype=torch.int32, device=dev)
+    pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(cap // moe_tile_rows(), dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    counts = torch.empty(2 * num_experts, dtype=torch.int32, device=dev)
+    _call("b200m_moe_align", idx.data_ptr(), pairs, num_experts, sorted_rows.data_ptr(), cap, pos_of.data_ptr(),
+          tile_expert.data_ptr(), num_tiles.data_ptr(), counts.data_ptr(), _stream())
+    return sorted_rows, pos_of, tile_expert, num_tiles
+
+
+def moe_gemm(A: torch.Tensor, sorted_rows, tile_expert, num_tiles, W: torch.Tensor, wgt: torch.Tensor | None = None, top: int = 1,
+             act: int = 0, out_f32: bool = False) -> torch.Tensor:
+    """W [experts, N, K].  With ``wgt``: row i is token (pair // top) of A times the pair's weight; else row i of A."""
+    assert A.dim() == 2 and A.stride(1) == 1 and W.dim() == 3 and W.is_contiguous() and A.shape[1] == W.shape[2]
+    is32 = _is32(A)
+    _same(is32, W)
+    cap = sorted_rows.numel()
+    out = torch.empty(cap, W.shape[1], dtype=torch.float32 if out_f32 else A.dtype, device=A.device)
+    _call("b200m_moe_gemm", A.data_ptr(), A.stride(0), sorted_rows.data_ptr(), _p(wgt), top, int(wgt is not None),
+          tile_expert.data_ptr(), num_tiles.data_ptr(), tile_expert.numel(), W.data_ptr(), W.shape[1], W.shape[2], out.data_ptr(),
+          int(out_f32), act, is32, _stream())
+    return out
+
+
+def moe_combine(rows: torch.Tensor, pos_of: torch.Tensor, top: int, n: int, shared: torch.Tensor | None = None,
+                gate_logit: torch.Tensor | None = None) -> torch.Tensor:
+    """rows fp32 [cap, width] -> fp32 [n, width]; gate_logit: fp32 column view [n] (any stride)."""
+    assert rows.dtype == torch.float32 and rows.is_contiguous()
+    width = rows.shape[1]
+    out = torch.empty(n, width, dtype=torch.float32, device=rows.device)
+    is32 = _is32(shared) if shared is not None else 1
+    gld = gate_logit.stride(0) if gate_logit is not None else 0
+    assert gate_logit is None or gate_logit.dtype == torch.float32
+    _call("b200m_moe_combine", rows.data_ptr(), pos_of.data_ptr(), top, _p(shared), _p(gate_logit), gld, out.data_ptr(), n, width,
+          is32, _stream())
+    return out

@@ -12,12 +12,14 @@ Field meaning (shapes as built by the runner, engine/model_runner.py:129-188 in 
   slot_mapping    int32   [T] cache slot of every new token, -1 = skip
   context_lens    int32   [B] keys visible to each decode row, 0 = CUDA-graph padding row
   block_tables    int32   [S or B, W] page ids, -1 padded; None = packed prefill without cache reads
+  state_slots     int32   [S or B] recurrent-state slot of every sequence (models with per-sequence state), else None
+  logit_rows      int32   [R] rows of the step whose logits are asked for; None = the last row of every sequence
 """
 from __future__ import annotations
 
 _FIELDS = ("is_prefill", "cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q", "max_seqlen_k",
-           "slot_mapping", "context_lens", "block_tables")
-_DEFAULTS = (False, None, None, 0, 0, None, None, None)
+           "slot_mapping", "context_lens", "block_tables", "state_slots", "logit_rows")
+_DEFAULTS = (False, None, None, 0, 0, None, None, None, None, None)
 
 
 class Context:
@@ -46,9 +48,9 @@ def get_context() -> Context:
 
 
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
-                slot_mapping=None, context_lens=None, block_tables=None) -> None:
+                slot_mapping=None, context_lens=None, block_tables=None, state_slots=None, logit_rows=None) -> None:
     _STEP.assign(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                 slot_mapping, context_lens, block_tables)
+                 slot_mapping, context_lens, block_tables, state_slots, logit_rows)
 
 
 def reset_context() -> None:
