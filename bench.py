@@ -537,7 +537,16 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the Tafopel hybrid decoder beside Qwen3 at equal "
+                         "size, with a per-kernel roofline table (profiles/hybrid_bench.py); one GPU")
+    ap.add_argument("--hybrid-sizes", default="w1024,w2048")
     args = ap.parse_args()
+    if args.hybrid:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
+        import hybrid_bench
+        hybrid_bench.main(["--sizes", args.hybrid_sizes])
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -58,12 +58,13 @@ int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, cons
 
 /* Multi-query attention of every head over the cached rows, causal, with a per-head sink logit in the softmax denominator.
  * q_lat [H, total_q, rank]: queries already mapped into the latent space; q_raw [total_q, H, q_head_stride]: the raw query
- * projection, whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank]. */
+ * projection, whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank].
+ * bf16 runs on the tensor cores (mma.sync over staged key tiles); fp32, or flags & 1, on the fp32 FMA pipe. */
 int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
                            const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                            const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                            int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                           int rot_dim, float scale, int is32, void* stream);
+                           int rot_dim, float scale, int is32, int flags, void* stream);
 
 /* ---- selective scan ------------------------------------------------------------------------------------------------ */
 

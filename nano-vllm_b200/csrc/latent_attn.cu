@@ -189,6 +189,239 @@ int launch_attn(const void* q_lat, const void* q_raw, int q_head_stride, int q_r
     return b200_launch_status(nullptr);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form (bf16): rows of a tile are (token, head) pairs of one sequence, 16 per warp, 4 warps; key tiles of 64 cache
+// rows are staged once per CTA and serve as B operand of S = Q K^T (row-major [key][dim]) and, through transposing loads, of
+// O += P V over their first `rank` columns.  One CTA covers at most MMA_OC output columns (grid.z walks wider latents and
+// recomputes S).  Scores, softmax statistics and O accumulate in fp32 registers; the sink seeds the running maximum and sum.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int MMA_BM = 64, MMA_BN = 64;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__host__ __device__ inline int mma_row_stride(int D) {
+    const int Dp = (D + 15) & ~15;
+    return Dp + (((Dp >> 3) & 1) ? 16 : 8);          // stride / 8 odd: the 8 rows of an ldmatrix hit 8 different 16-byte bank groups
+}
+
+template <int NT_O>
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(
+    const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_raw, int q_head_stride, int q_rot_off,
+    const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
+    const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
+    const float* __restrict__ sink, const float* __restrict__ cos_sin, int rope_dims, __nv_bfloat16* __restrict__ out,
+    int total_q, int H, int rank, int rot_dim, float scale) {
+    B200_PDL_SYNC();
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int D = rank + rot_dim, Dp = (D + 15) & ~15, DS = mma_row_stride(D);
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
+    __nv_bfloat16* Ks = Qs + MMA_BM * DS;
+    const int s = blockIdx.y;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    const int nrows = sp.qlen * H, row0 = blockIdx.x * MMA_BM;
+    if (row0 >= nrows) return;
+    const int rc0 = blockIdx.z * (NT_O * 8);
+    const int first = sp.klen - sp.qlen;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+
+    // ---- stage Q (rotating its last rot_dim elements), zero the padding of both tiles ----
+    for (int e = tid; e < MMA_BM * DS; e += 128) {
+        const int r = e / DS, c = e - r * DS;
+        const int rr = row0 + r;
+        __nv_bfloat16 v = zero;
+        if (rr < nrows && c < D) {
+            const int i = rr / H, h = rr - i * H;
+            const int64_t tok = sp.q0 + i;
+            if (c < rank) {
+                v = q_lat[((int64_t)h * total_q + tok) * rank + c];
+            } else {
+                const int cr = c - rank;
+                const __nv_bfloat16* qr = q_raw + (tok * H + h) * q_head_stride + q_rot_off;
+                if (cr < rope_dims) {
+                    const float* cs = cos_sin + (int64_t)(first + i) * rope_dims;
+                    const int half = rope_dims >> 1, p = cr >> 1;
+                    const float u = __bfloat162float(qr[2 * p]), w = __bfloat162float(qr[2 * p + 1]);
+                    v = __float2bfloat16_rn((cr & 1) ? (w * cs[p] + u * cs[half + p]) : (u * cs[p] - w * cs[half + p]));
+                } else {
+                    v = qr[cr];
+                }
+            }
+        }
+        Qs[e] = v;
+        if (c >= Dp) Ks[e] = zero;
+    }
+    // rows of this warp: g and g + 8 of its 16
+    float m_run[2], l_run[2];
+    int pos_row[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int rr = row0 + warp * 16 + g + 8 * k;
+        const bool live = rr < nrows;
+        const int i = live ? rr / H : 0;
+        pos_row[k] = live ? first + i : -1;
+        m_run[k] = live ? sink[rr - i * H] : 0.f;
+        l_run[k] = 1.0f;
+    }
+    float o[NT_O][4];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const int np_used = min(NT_O / 2, (rank - rc0 + 15) / 16);       // pairs of 8-column tiles that hold real output columns
+    const int i_hi = min(sp.qlen - 1, (row0 + MMA_BM - 1) / H);
+    const int kmax = first + i_hi + 1;
+    const int warp_pos_max = first + min(sp.qlen - 1, (row0 + warp * 16 + 15) / H);
+    const bool warp_live = row0 + warp * 16 < nrows;
+    const int32_t* bt = block_tables + (int64_t)s * bt_stride;
+    const uint32_t qs_base = smem_u32(Qs), ks_base = smem_u32(Ks);
+    const bool vec = (D & 7) == 0;
+    for (int j0 = 0; j0 < kmax; j0 += MMA_BN) {
+        __syncthreads();
+        // ---- stage 64 cache rows ----
+        if (vec) {
+            const int c8n = Dp >> 3;
+            for (int e = tid; e < MMA_BN * c8n; e += 128) {
+                const int r = e / c8n, c = (e - r * c8n) << 3;
+                const int j = j0 + r;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (j < kmax && c < D) {
+                    const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
+                    v = *reinterpret_cast<const uint4*>(cache + slot * D + c);
+                }
+                *reinterpret_cast<uint4*>(Ks + r * DS + c) = v;
+            }
+        } else {
+            for (int e = tid; e < MMA_BN * Dp; e += 128) {
+                const int r = e / Dp, c = e - r * Dp;
+                const int j = j0 + r;
+                __nv_bfloat16 v = zero;
+                if (j < kmax && c < D) {
+                    const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
+                    v = cache[slot * D + c];
+                }
+                Ks[r * DS + c] = v;
+            }
+        }
+        __syncthreads();
+        if (!warp_live || j0 > warp_pos_max) continue;
+        // ---- S = Q K^T (16 x 64 per warp) ----
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+        const uint32_t a_addr = qs_base + (uint32_t)(((warp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
+        const uint32_t b_addr = ks_base + (uint32_t)((((lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
+        for (int kk = 0; kk < Dp; kk += 16) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(b_addr + (uint32_t)((np * 16 * DS + kk) * 2), b0, b1, b2, b3);
+                mma_bf16(sc[2 * np], a0, a1, a2, a3, b0, b1);
+                mma_bf16(sc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        // ---- mask, online softmax ----
+        float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = j0 + n * 8 + 2 * t4 + (e & 1);
+                const int k = e >> 1;
+                const float v = (key <= pos_row[k]) ? sc[n][e] * scale : -INFINITY;
+                sc[n][e] = v;
+                mx[k] = fmaxf(mx[k], v);
+            }
+        float alpha[2], psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 1));
+            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
+            alpha[k] = __expf(m_run[k] - mx[k]);
+            m_run[k] = mx[k];
+        }
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float p0 = __expf(sc[n][0] - mx[0]), p1 = __expf(sc[n][1] - mx[0]);
+            const float p2 = __expf(sc[n][2] - mx[1]), p3 = __expf(sc[n][3] - mx[1]);
+            psum[0] += p0 + p1;
+            psum[1] += p2 + p3;
+            pa[n >> 1][(n & 1) * 2] = pack_bf16x2(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            psum[k] += __shfl_xor_sync(0xffffffffu, psum[k], 1);
+            psum[k] += __shfl_xor_sync(0xffffffffu, psum[k], 2);
+            l_run[k] = l_run[k] * alpha[k] + psum[k];
+        }
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) {
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1];
+            o[n][3] *= alpha[1];
+        }
+        // ---- O += P V ----
+        const uint32_t v_addr = ks_base + (uint32_t)((((lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int np = 0; np < NT_O / 2; ++np) {
+                if (np < np_used) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_t(v_addr + (uint32_t)((kk * 16 * DS + np * 16) * 2), b0, b1, b2, b3);
+                    mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+                    mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+                }
+            }
+        }
+    }
+    // ---- write ----
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int rr = row0 + warp * 16 + g + 8 * k;
+        if (rr >= nrows) continue;
+        const int i = rr / H, h = rr - i * H;
+        const float inv = 1.0f / l_run[k];
+        __nv_bfloat16* dst = out + ((int64_t)h * total_q + sp.q0 + i) * rank;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) {
+            const int c = rc0 + n * 8 + 2 * t4;
+            if (c < rank) dst[c] = __float2bfloat16_rn(o[n][2 * k] * inv);
+            if (c + 1 < rank) dst[c + 1] = __float2bfloat16_rn(o[n][2 * k + 1] * inv);
+        }
+    }
+}
+
+template <int NT_O>
+int launch_attn_mma(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                    const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
+                    const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
+                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, cudaStream_t stream) {
+    const int DS = mma_row_stride(rank + rot_dim);
+    const size_t smem = (size_t)(MMA_BM + MMA_BN) * DS * sizeof(__nv_bfloat16);
+    int rc = ensure_smem(latent_attn_mma_kernel<NT_O>, smem);
+    if (rc != B200_OK) return rc;
+    dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, (rank + NT_O * 8 - 1) / (NT_O * 8));
+    using bf = __nv_bfloat16;
+    B200_LAUNCH((latent_attn_mma_kernel<NT_O>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
+                q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
+                sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale);
+    return b200_launch_status(nullptr);
+}
+
 }  // namespace
 
 extern "C" int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, const float* cos_sin, int rope_dims,
@@ -207,7 +440,7 @@ extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int 
                                       const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                                       const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                                       int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                                      int rot_dim, float scale, int is32, void* stream) {
+                                      int rot_dim, float scale, int is32, int flags, void* stream) {
     if (!q_lat || !q_raw || !cache || !block_tables || !sink || !cos_sin || !out) return B200_EINVAL;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (total_q < 0 || num_seqs < 0 || num_heads <= 0 || rank <= 0 || rot_dim < 0 || block_size <= 0) return B200_EINVAL;
@@ -215,6 +448,13 @@ extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int 
     if (rank > 512) return B200_EUNSUPPORTED;
     if (total_q == 0 || num_seqs == 0 || max_q <= 0) return B200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!is32 && !(flags & 1)) {         // bf16: tensor cores; 128 output columns per CTA when the latent fits, else 256 per pass
+        if (rank <= 128)
+            return launch_attn_mma<16>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                       ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, st);
+        return launch_attn_mma<32>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, st);
+    }
 #define LA_GO(N)                                                                                                              \
     B200M_DISPATCH(is32, return (launch_attn<T, N>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride,     \
                                                    block_size, cu_q, cu_k, ctx_lens, sink, cos_sin, rope_dims, out, total_q,  \

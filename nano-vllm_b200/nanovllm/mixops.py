@@ -130,8 +130,8 @@ def latent_store(dkv: torch.Tensor, norm_w: torch.Tensor, cos_sin: torch.Tensor,
 
 def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, cache: torch.Tensor, block_tables: torch.Tensor,
                      block_size: int, spans: StepSpans, sink: torch.Tensor, cos_sin: torch.Tensor, scale: float,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
-    """q_lat [H, n, rank], q_raw [n, H, head_stride] -> [H, n, rank]."""
+                     out: torch.Tensor | None = None, fma: bool = False) -> torch.Tensor:
+    """q_lat [H, n, rank], q_raw [n, H, head_stride] -> [H, n, rank].  bf16 runs on the tensor cores unless ``fma``."""
     H, n, rank = q_lat.shape
     rot_dim = cache.shape[-1] - rank
     assert q_lat.is_contiguous() and q_raw.is_contiguous() and q_raw.shape[:2] == (n, H) and cache.is_contiguous()
@@ -143,7 +143,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, c
     _call("b200m_latent_attention", q_lat.data_ptr(), q_raw.data_ptr(), q_raw.shape[2], q_rot_off, cache.data_ptr(),
           block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
           sink.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1], out.data_ptr(), n, spans.num_seqs, spans.max_q, H, rank,
-          rot_dim, scale, is32, _stream())
+          rot_dim, scale, is32, int(fma), _stream())
     return out
 
 
