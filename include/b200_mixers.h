@@ -59,12 +59,14 @@ int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, cons
 /* Multi-query attention of every head over the cached rows, causal, with a per-head sink logit in the softmax denominator.
  * q_lat [H, total_q, rank]: queries already mapped into the latent space; q_raw [total_q, H, q_head_stride]: the raw query
  * projection, whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank].
- * bf16 runs on the tensor cores (mma.sync over staged key tiles); fp32, or flags & 1, on the fp32 FMA pipe. */
+ * bf16 runs on the tensor cores (mma.sync over staged key tiles); fp32, or flags & 1, on the fp32 FMA pipe.
+ * splits > 1 (bf16 decode steps only, ignored elsewhere): the keys of every sequence are shared out over `splits` CTAs whose
+ * partial results, fp32 [num_seqs, 4 * splits, num_heads, rank + 2] in `part`, a second launch merges. */
 int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
                            const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                            const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                            int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                           int rot_dim, float scale, int is32, int flags, void* stream);
+                           int rot_dim, float scale, int is32, int flags, int splits, float* part, void* stream);
 
 /* ---- selective scan ------------------------------------------------------------------------------------------------ */
 
@@ -76,11 +78,13 @@ int b200m_causal_conv(const void* x, int64_t x_stride, const void* w, const void
                       int num_seqs, int max_q, int channels, int taps, int is32, void* stream);
 
 /* S <- exp(dt A) S + dt u B;  y = (S C + D u) * silu(z), dt = softplus(dt_raw + dt_bias); A [channels, nstate] fp32;
- * state [slots, channels, nstate] fp32, started from zero when the sequence has no tokens behind it. */
+ * state [slots, channels, nstate] fp32, started from zero when the sequence has no tokens behind it.
+ * With a workspace (ws: fp32, num_seqs * ceil(max_q / chunk_len) * channels * (nstate + 1)) portions longer than chunk_len
+ * run as chunks in parallel (local pass, carry pass, output pass: three launches); ws = NULL: one launch, serial per sequence. */
 int b200m_selective_scan(const void* u, const void* dt_raw, const void* dt_bias, const float* A, const void* Bm, const void* Cm,
                          int64_t bc_stride, const void* Dv, const void* z, int64_t z_stride, float* state,
                          const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, void* y,
-                         int num_seqs, int channels, int nstate, int is32, void* stream);
+                         int num_seqs, int channels, int nstate, int chunk_len, int max_q, float* ws, int is32, void* stream);
 
 /* ---- routed experts ------------------------------------------------------------------------------------------------ */
 

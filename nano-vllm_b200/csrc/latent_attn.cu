@@ -214,13 +214,15 @@ __host__ __device__ inline int mma_row_stride(int D) {
     return Dp + (((Dp >> 3) & 1) ? 16 : 8);          // stride / 8 odd: the 8 rows of an ldmatrix hit 8 different 16-byte bank groups
 }
 
-template <int NT_O>
+// WS (single-token steps with at most 16 heads): the four warps share the 16 query rows and each takes 16 of a tile's 64 keys,
+// leaving one partial per (split, warp).
+template <int NT_O, bool WS>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_raw, int q_head_stride, int q_rot_off,
     const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
     const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
     const float* __restrict__ sink, const float* __restrict__ cos_sin, int rope_dims, __nv_bfloat16* __restrict__ out,
-    int total_q, int H, int rank, int rot_dim, float scale) {
+    int total_q, int H, int rank, int rot_dim, float scale, int splits, float* __restrict__ part) {
     B200_PDL_SYNC();
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = rank + rot_dim, Dp = (D + 15) & ~15, DS = mma_row_stride(D);
@@ -230,7 +232,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     const int nrows = sp.qlen * H, row0 = blockIdx.x * MMA_BM;
     if (row0 >= nrows) return;
-    const int rc0 = blockIdx.z * (NT_O * 8);
+    // grid.z = (column chunk, key split): with splits > 1 (single-token steps) every CTA covers a contiguous share of the
+    // key tiles and leaves unnormalised (acc, max, sum) partials for latent_merge_kernel
+    const int split = blockIdx.z % splits;
+    const int rc0 = (blockIdx.z / splits) * (NT_O * 8);
     const int first = sp.klen - sp.qlen;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
@@ -262,16 +267,23 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         if (c >= Dp) Ks[e] = zero;
     }
     // rows of this warp: g and g + 8 of its 16
+    constexpr int NKT = WS ? 2 : 8;                       // 8-key tiles of S per warp
+    const int rwarp = WS ? 0 : warp;                      // which 16 rows of the tile this warp owns
+    const int koff = WS ? warp * 16 : 0;                  // first key of the tile this warp looks at
     float m_run[2], l_run[2];
     int pos_row[2];
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
-        const int rr = row0 + warp * 16 + g + 8 * k;
+        const int rr = row0 + rwarp * 16 + g + 8 * k;
         const bool live = rr < nrows;
         const int i = live ? rr / H : 0;
         pos_row[k] = live ? first + i : -1;
         m_run[k] = live ? sink[rr - i * H] : 0.f;
         l_run[k] = 1.0f;
+        if (split > 0 || (WS && warp > 0)) {              // the sink is counted once, by the first partial
+            m_run[k] = -1e30f;
+            l_run[k] = 0.f;
+        }
     }
     float o[NT_O][4];
 #pragma unroll
@@ -279,12 +291,18 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int np_used = min(NT_O / 2, (rank - rc0 + 15) / 16);       // pairs of 8-column tiles that hold real output columns
     const int i_hi = min(sp.qlen - 1, (row0 + MMA_BM - 1) / H);
     const int kmax = first + i_hi + 1;
-    const int warp_pos_max = first + min(sp.qlen - 1, (row0 + warp * 16 + 15) / H);
-    const bool warp_live = row0 + warp * 16 < nrows;
+    const int warp_pos_max = first + min(sp.qlen - 1, (row0 + rwarp * 16 + 15) / H);
+    const bool warp_live = row0 + rwarp * 16 < nrows;
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
     const uint32_t qs_base = smem_u32(Qs), ks_base = smem_u32(Ks);
     const bool vec = (D & 7) == 0;
-    for (int j0 = 0; j0 < kmax; j0 += MMA_BN) {
+    int j_begin = 0, j_end = kmax;
+    if (splits > 1) {
+        const int tiles = (kmax + MMA_BN - 1) / MMA_BN, per = (tiles + splits - 1) / splits;
+        j_begin = split * per * MMA_BN;
+        j_end = min(kmax, (split + 1) * per * MMA_BN);
+    }
+    for (int j0 = j_begin; j0 < j_end; j0 += MMA_BN) {
         __syncthreads();
         // ---- stage 64 cache rows ----
         if (vec) {
@@ -312,18 +330,18 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             }
         }
         __syncthreads();
-        if (!warp_live || j0 > warp_pos_max) continue;
-        // ---- S = Q K^T (16 x 64 per warp) ----
-        float sc[8][4];
+        if (!warp_live || j0 + koff > warp_pos_max) continue;
+        // ---- S = Q K^T (16 rows x NKT * 8 keys per warp) ----
+        float sc[NKT][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-        const uint32_t a_addr = qs_base + (uint32_t)(((warp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
-        const uint32_t b_addr = ks_base + (uint32_t)((((lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
+        for (int n = 0; n < NKT; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+        const uint32_t a_addr = qs_base + (uint32_t)(((rwarp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
+        const uint32_t b_addr = ks_base + (uint32_t)(((koff + (lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
         for (int kk = 0; kk < Dp; kk += 16) {
             uint32_t a0, a1, a2, a3;
             ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {
+            for (int np = 0; np < NKT / 2; ++np) {
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4(b_addr + (uint32_t)((np * 16 * DS + kk) * 2), b0, b1, b2, b3);
                 mma_bf16(sc[2 * np], a0, a1, a2, a3, b0, b1);
@@ -333,10 +351,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         // ---- mask, online softmax ----
         float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
+        for (int n = 0; n < NKT; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int key = j0 + n * 8 + 2 * t4 + (e & 1);
+                const int key = j0 + koff + n * 8 + 2 * t4 + (e & 1);
                 const int k = e >> 1;
                 const float v = (key <= pos_row[k]) ? sc[n][e] * scale : -INFINITY;
                 sc[n][e] = v;
@@ -350,9 +368,9 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             alpha[k] = __expf(m_run[k] - mx[k]);
             m_run[k] = mx[k];
         }
-        uint32_t pa[4][4];
+        uint32_t pa[NKT / 2][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < NKT; ++n) {
             const float p0 = __expf(sc[n][0] - mx[0]), p1 = __expf(sc[n][1] - mx[0]);
             const float p2 = __expf(sc[n][2] - mx[1]), p3 = __expf(sc[n][3] - mx[1]);
             psum[0] += p0 + p1;
@@ -374,9 +392,9 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             o[n][3] *= alpha[1];
         }
         // ---- O += P V ----
-        const uint32_t v_addr = ks_base + (uint32_t)((((lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
+        const uint32_t v_addr = ks_base + (uint32_t)(((koff + (lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < NKT / 2; ++kk) {
 #pragma unroll
             for (int np = 0; np < NT_O / 2; ++np) {
                 if (np < np_used) {
@@ -389,6 +407,26 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         }
     }
     // ---- write ----
+    if (splits > 1) {                                     // rows are heads here (one token per sequence)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int rr = row0 + rwarp * 16 + g + 8 * k;
+            if (rr >= nrows) continue;
+            const int np = WS ? splits * 4 : splits, pi = WS ? split * 4 + warp : split;
+            float* dst = part + (((int64_t)s * np + pi) * H + rr) * (rank + 2);
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n) {
+                const int c = rc0 + n * 8 + 2 * t4;
+                if (c < rank) dst[c] = o[n][2 * k];
+                if (c + 1 < rank) dst[c + 1] = o[n][2 * k + 1];
+            }
+            if (rc0 == 0 && t4 == 0) {
+                dst[rank] = m_run[k];
+                dst[rank + 1] = l_run[k];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         const int rr = row0 + warp * 16 + g + 8 * k;
@@ -405,21 +443,60 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     }
 }
 
+// out[h, s, :] = sum_p e^(m_p - M) acc_p / sum_p e^(m_p - M) l_p over the key splits of a single-token step
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part, const int32_t* __restrict__ ctx_lens, int splits,
+                                                           int H, int rank, int total_q, __nv_bfloat16* __restrict__ out) {
+    B200_PDL_SYNC();
+    const int s = blockIdx.x, h = blockIdx.y;
+    if (ctx_lens[s] <= 0) return;
+    const float* base = part + ((int64_t)s * splits * H + h) * (rank + 2);
+    const int64_t step = (int64_t)H * (rank + 2);
+    float M = -1e30f;
+    for (int p = 0; p < splits; ++p) M = fmaxf(M, base[p * step + rank]);
+    float L = 0.f;
+    for (int p = 0; p < splits; ++p) L += __expf(base[p * step + rank] - M) * base[p * step + rank + 1];
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float a = 0.f;
+        for (int p = 0; p < splits; ++p) a = fmaf(__expf(base[p * step + rank] - M), base[p * step + c], a);
+        out[((int64_t)h * total_q + s) * rank + c] = __float2bfloat16_rn(a * inv);
+    }
+}
+
+template <int NT_O, bool WS>
+int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                    const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
+                    const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
+                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+    const int DS = mma_row_stride(rank + rot_dim);
+    if (splits < 1 || max_q != 1 || cu_q != nullptr || part == nullptr || H > MMA_BM) splits = 1;
+    const size_t smem = (size_t)(MMA_BM + MMA_BN) * DS * sizeof(__nv_bfloat16);
+    int rc = ensure_smem(latent_attn_mma_kernel<NT_O, WS>, smem);
+    if (rc != B200_OK) return rc;
+    dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, ((rank + NT_O * 8 - 1) / (NT_O * 8)) * splits);
+    using bf = __nv_bfloat16;
+    B200_LAUNCH((latent_attn_mma_kernel<NT_O, WS>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
+                q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
+                sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale, splits, part);
+    rc = b200_launch_status(nullptr);
+    if (rc != B200_OK || splits == 1) return rc;
+    B200_LAUNCH((latent_merge_kernel), dim3(num_seqs, H), 128, 0, stream, (const float*)part, ctx_lens, WS ? splits * 4 : splits, H, rank,
+                total_q, static_cast<bf*>(out));
+    return b200_launch_status(nullptr);
+}
+
 template <int NT_O>
 int launch_attn_mma(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
                     const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                     const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
-                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, cudaStream_t stream) {
-    const int DS = mma_row_stride(rank + rot_dim);
-    const size_t smem = (size_t)(MMA_BM + MMA_BN) * DS * sizeof(__nv_bfloat16);
-    int rc = ensure_smem(latent_attn_mma_kernel<NT_O>, smem);
-    if (rc != B200_OK) return rc;
-    dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, (rank + NT_O * 8 - 1) / (NT_O * 8));
-    using bf = __nv_bfloat16;
-    B200_LAUNCH((latent_attn_mma_kernel<NT_O>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
-                q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
-                sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale);
-    return b200_launch_status(nullptr);
+                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+    if (splits > 1 && max_q == 1 && cu_q == nullptr && part != nullptr && H <= 16)
+        return launch_attn_mma_ws<NT_O, true>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                              ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
+                                              splits, part, stream);
+    return launch_attn_mma_ws<NT_O, false>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                           ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
+                                           splits, part, stream);
 }
 
 }  // namespace
@@ -440,7 +517,7 @@ extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int 
                                       const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                                       const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                                       int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                                      int rot_dim, float scale, int is32, int flags, void* stream) {
+                                      int rot_dim, float scale, int is32, int flags, int splits, float* part, void* stream) {
     if (!q_lat || !q_raw || !cache || !block_tables || !sink || !cos_sin || !out) return B200_EINVAL;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (total_q < 0 || num_seqs < 0 || num_heads <= 0 || rank <= 0 || rot_dim < 0 || block_size <= 0) return B200_EINVAL;
@@ -451,9 +528,9 @@ extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int 
     if (!is32 && !(flags & 1)) {         // bf16: tensor cores; 128 output columns per CTA when the latent fits, else 256 per pass
         if (rank <= 128)
             return launch_attn_mma<16>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                       ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, st);
+                                       ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, splits, part, st);
         return launch_attn_mma<32>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, st);
+                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, splits, part, st);
     }
 #define LA_GO(N)                                                                                                              \
     B200M_DISPATCH(is32, return (launch_attn<T, N>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride,     \

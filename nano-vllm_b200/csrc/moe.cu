@@ -142,6 +142,133 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form of the grouped GEMM (bf16): one 32-row tile of one expert x 128 output columns per CTA, K in steps of 64
+// through a two-stage shared-memory ring (weights by cp.async, the gathered / weighted input rows through registers),
+// mma.sync m16n8k16 with fp32 accumulation.  Needs K % 8 == 0 and 16-byte aligned rows; other shapes take the FMA kernel.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int MM_BN = 128, MM_BK = 64, MM_LD = MM_BK + 8;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t a_stride,
+                                                           const int32_t* __restrict__ sorted_rows, const float* __restrict__ wgt, int top,
+                                                           bool gather, const int32_t* __restrict__ tile_expert,
+                                                           const int32_t* __restrict__ num_tiles, const __nv_bfloat16* __restrict__ W, int N,
+                                                           int K, TO* __restrict__ C, int act) {
+    B200_PDL_SYNC();
+    const int tile = blockIdx.y;
+    if (tile >= num_tiles[0]) return;
+    __shared__ __align__(16) __nv_bfloat16 As[2][MG_BM][MM_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[2][MM_BN][MM_LD];
+    __shared__ int src[MG_BM];
+    __shared__ float sc[MG_BM];
+    const int e = tile_expert[tile];
+    const __nv_bfloat16* We = W + (int64_t)e * N * K;
+    const int row0 = tile * MG_BM, col0 = blockIdx.x * MM_BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MG_BM) {
+        const int p = sorted_rows[row0 + tid];
+        src[tid] = p < 0 ? -1 : (gather ? p / top : row0 + tid);
+        sc[tid] = (p >= 0 && gather) ? wgt[p] : 1.0f;
+    }
+    __syncthreads();
+    auto load_stage = [&](int st, int k0) {
+        for (int i = tid; i < MM_BN * (MM_BK / 8); i += 128) {          // weights: 128 rows x 8 chunks of 16 bytes
+            const int r = i >> 3, c = (i & 7) << 3;
+            const bool ok = col0 + r < N && k0 + c < K;
+            cp_async16(smem_u32(&Bs[st][r][c]), ok ? (const void*)(We + (int64_t)(col0 + r) * K + k0 + c) : (const void*)We, ok ? 16 : 0);
+        }
+        for (int i = tid; i < MG_BM * (MM_BK / 8); i += 128) {          // input rows: gathered, weighted, rounded
+            const int r = i >> 3, c = (i & 7) << 3;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (src[r] >= 0 && k0 + c < K) {
+                v = *reinterpret_cast<const uint4*>(A + (int64_t)src[r] * a_stride + k0 + c);
+                if (gather) {
+                    float f[8];
+                    unpack8(v, f);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) f[q] *= sc[r];
+                    v = pack8(f);
+                }
+            }
+            *reinterpret_cast<uint4*>(&As[st][r][c]) = v;
+        }
+        cp_async_commit();
+    };
+    float acc[2][4][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
+    const int nk = (K + MM_BK - 1) / MM_BK;
+    load_stage(0, 0);
+    for (int it = 0; it < nk; ++it) {
+        const int st = it & 1;
+        if (it + 1 < nk) {
+            load_stage(st ^ 1, (it + 1) * MM_BK);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t a_base = smem_u32(&As[st][lane & 15][(lane >> 4) << 3]);
+        const uint32_t b_base = smem_u32(&Bs[st][warp * 32 + (lane & 7) + ((lane >> 4) << 3)][((lane >> 3) & 1) << 3]);
+#pragma unroll
+        for (int kk = 0; kk < MM_BK; kk += 16) {
+            uint32_t a[2][4];
+            ldsm4(a_base + kk * 2, a[0][0], a[0][1], a[0][2], a[0][3]);
+            ldsm4(a_base + (16 * MM_LD + kk) * 2, a[1][0], a[1][1], a[1][2], a[1][3]);
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldsm4(b_base + (np * 16 * MM_LD + kk) * 2, b0, b1, b2, b3);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma16816(acc[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+                    mma16816(acc[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int row = mt * 16 + g + 8 * hh;
+            if (src[row] < 0) continue;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int col = col0 + warp * 32 + nt * 8 + 2 * t4 + q;
+                    if (col >= N) continue;
+                    float v = acc[mt][nt][2 * hh + q];
+                    if (act == 1) {
+                        v = fmaxf(v, 0.f);
+                        v = v * v;
+                    }
+                    stf(C + (int64_t)(row0 + row) * N + col, v);
+                }
+        }
+}
+
 // out[t, :] = sum_k rows[pos_of[t * top + k], :] + sigmoid(gate_logit[t]) * shared[t, :]
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ pos_of, int top,
@@ -186,6 +313,18 @@ extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* so
     if (gather && (!wgt || top <= 0)) return B200_EINVAL;
     if (max_tiles == 0) return B200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tc = !is32 && (K % 8 == 0) && (a_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) % 16 == 0);
+    if (tc) {
+        dim3 g2((N + MM_BN - 1) / MM_BN, max_tiles);
+        using bf = __nv_bfloat16;
+        if (out_f32)
+            B200_LAUNCH((moe_gemm_mma_kernel<float>), g2, 128, 0, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
+                        tile_expert, num_tiles, static_cast<const bf*>(W), N, K, static_cast<float*>(C), act);
+        else
+            B200_LAUNCH((moe_gemm_mma_kernel<bf>), g2, 128, 0, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
+                        tile_expert, num_tiles, static_cast<const bf*>(W), N, K, static_cast<bf*>(C), act);
+        return b200_launch_status(nullptr);
+    }
     dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
     if (out_f32) {
         B200M_DISPATCH(is32, B200_LAUNCH((moe_gemm_kernel<T, float>), grid, 256, 0, st, static_cast<const T*>(A), a_stride, sorted_rows,

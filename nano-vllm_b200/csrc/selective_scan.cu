@@ -9,7 +9,10 @@
 //   causal_conv_kernel      : depthwise causal convolution + bias + SiLU over a varlen batch, history taken from the slot
 //   conv_state_update_kernel: the slot's history after the step (run after the convolution: it overwrites what that reads)
 //   selective_scan_kernel   : the recurrence, serial over a sequence's tokens, 4 lanes per channel holding the state in
-//                             registers; one token per sequence is the decode case of the same kernel
+//                             registers; one token per sequence is the decode case of the same kernel.  Long portions run
+//                             it three times over chunks of tokens: (1) every chunk from a zero state, keeping its end state
+//                             and sum of step sizes; (2) scan_carry_kernel chains the chunks, S_in[z+1] = exp(A sum_dt[z])
+//                             S_in[z] + S_end[z]; (3) every chunk again from its true start state, now writing y
 #include "mix_common.cuh"
 
 namespace {
@@ -73,7 +76,9 @@ constexpr int SCAN_LANES = 4;          // lanes that share one channel's state
 constexpr int SCAN_CH = 32;            // channels per CTA (128 threads)
 
 // NPL states per lane: state n = k * SCAN_LANES + sub, k < NPL.
-template <typename T, int NPL>
+// MODE 0: whole portion, slot to slot.  1: chunk from zero, end state and sum of dt to the workspace.  3: chunk from the
+// workspace's start state, y out.
+template <typename T, int NPL, int MODE>
 __global__ void __launch_bounds__(SCAN_LANES * SCAN_CH) selective_scan_kernel(
     const T* __restrict__ u,            // [n, channels]
     const T* __restrict__ dt_raw,       // [n, channels]
@@ -84,11 +89,15 @@ __global__ void __launch_bounds__(SCAN_LANES * SCAN_CH) selective_scan_kernel(
     const T* __restrict__ z, int64_t z_stride,                               // [n, channels] with a row stride
     float* __restrict__ state,          // [slots, channels, nstate]
     const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k,
-    const int32_t* __restrict__ ctx_lens, T* __restrict__ y, int channels, int nstate) {
+    const int32_t* __restrict__ ctx_lens, T* __restrict__ y, int channels, int nstate, int chunk_len, int nchunks,
+    float* __restrict__ ws_state, float* __restrict__ ws_sumdt) {
     B200_PDL_SYNC();
     const int s = blockIdx.y;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     if (sp.qlen <= 0) return;
+    const int i_begin = MODE == 0 ? 0 : blockIdx.z * chunk_len;
+    if (i_begin >= sp.qlen) return;
+    const int i_end = MODE == 0 ? sp.qlen : min(sp.qlen, i_begin + chunk_len);
     const int sub = threadIdx.x % SCAN_LANES;
     const int c = blockIdx.x * SCAN_CH + threadIdx.x / SCAN_LANES;
     const bool live = c < channels;
@@ -99,30 +108,62 @@ __global__ void __launch_bounds__(SCAN_LANES * SCAN_CH) selective_scan_kernel(
 #pragma unroll
     for (int k = 0; k < NPL; ++k) {
         const int n = k * SCAN_LANES + sub;
-        S[k] = (has_hist && n < nstate) ? st[n] : 0.f;
+        if (MODE == 0) S[k] = (has_hist && n < nstate) ? st[n] : 0.f;
+        else if (MODE == 1) S[k] = 0.f;
+        else S[k] = n < nstate ? ws_state[(((int64_t)s * nchunks + blockIdx.z) * channels + cc) * nstate + n] : 0.f;
         a[k] = n < nstate ? A[(int64_t)cc * nstate + n] : 0.f;
     }
     const float bias = ldf(dt_bias + cc), dskip = ldf(Dv + cc);
-    for (int i = 0; i < sp.qlen; ++i) {
-        const int64_t t = sp.q0 + i;
-        const float uu = ldf(u + t * channels + cc);
-        const float dt = softplusf_(ldf(dt_raw + t * channels + cc) + bias);
-        const float du = dt * uu;
-        float part = 0.f;
+    // Tokens in groups of TB: all loads of a group are issued before its (serial) arithmetic, so the recurrence waits for
+    // memory once per group instead of once per token.
+    constexpr int TB = NPL <= 4 ? 8 : (NPL <= 8 ? 4 : 2);
+    float sumdt = 0.f;
+    for (int i0 = i_begin; i0 < i_end; i0 += TB) {
+        float uu[TB], dr[TB], zz[TB], bb[TB][NPL], cv[TB][NPL];
 #pragma unroll
-        for (int k = 0; k < NPL; ++k) {
-            const int n = k * SCAN_LANES + sub;
-            if (n < nstate) {
-                S[k] = fmaf(expf(dt * a[k]), S[k], du * ldf(Bm + t * bc_stride + n));
-                part = fmaf(S[k], ldf(Cm + t * bc_stride + n), part);
+        for (int j = 0; j < TB; ++j) {
+            if (i0 + j >= i_end) {                          // past the portion: nothing to fetch (a single-token step has one row)
+                uu[j] = dr[j] = zz[j] = 0.f;
+#pragma unroll
+                for (int k = 0; k < NPL; ++k) bb[j][k] = cv[j][k] = 0.f;
+                continue;
+            }
+            const int64_t t = sp.q0 + i0 + j;
+            uu[j] = ldf(u + t * channels + cc);
+            dr[j] = ldf(dt_raw + t * channels + cc);
+            zz[j] = ldf(z + t * z_stride + cc);
+#pragma unroll
+            for (int k = 0; k < NPL; ++k) {
+                const int n = min(k * SCAN_LANES + sub, nstate - 1);
+                bb[j][k] = ldf(Bm + t * bc_stride + n);
+                cv[j][k] = ldf(Cm + t * bc_stride + n);
             }
         }
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        if (live && sub == 0) {
-            const float zz = ldf(z + t * z_stride + cc);
-            stf(y + t * channels + cc, (part + dskip * uu) * siluf_(zz));
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            if (i0 + j < i_end) {
+                const float dt = softplusf_(dr[j] + bias);
+                sumdt += dt;
+                const float du = dt * uu[j];
+                float part = 0.f;
+#pragma unroll
+                for (int k = 0; k < NPL; ++k) {
+                    if (k * SCAN_LANES + sub < nstate) {
+                        S[k] = fmaf(expf(dt * a[k]), S[k], du * bb[j][k]);
+                        part = fmaf(S[k], cv[j][k], part);
+                    }
+                }
+                if (MODE == 1) continue;
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                part += __shfl_xor_sync(0xffffffffu, part, 2);
+                if (live && sub == 0) stf(y + (sp.q0 + i0 + j) * (int64_t)channels + cc, (part + dskip * uu[j]) * siluf_(zz[j]));
+            }
         }
+    }
+    if (MODE == 3) return;
+    if (MODE == 1) {
+        st = ws_state + (((int64_t)s * nchunks + blockIdx.z) * channels + cc) * nstate;
+        if (live && sub == 0) ws_sumdt[((int64_t)s * nchunks + blockIdx.z) * channels + cc] = sumdt;
     }
     if (live) {
 #pragma unroll
@@ -131,6 +172,33 @@ __global__ void __launch_bounds__(SCAN_LANES * SCAN_CH) selective_scan_kernel(
             if (n < nstate) st[n] = S[k];
         }
     }
+}
+
+// Chains the chunks of every sequence: ws_state[z] goes from "end state of chunk z started at zero" to "state at the start
+// of chunk z"; the slot receives the state after the last chunk.
+__global__ void __launch_bounds__(256) scan_carry_kernel(const float* __restrict__ A, float* __restrict__ state,
+                                                         const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q,
+                                                         const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, int channels,
+                                                         int nstate, int chunk_len, int nchunks, float* __restrict__ ws_state,
+                                                         const float* __restrict__ ws_sumdt) {
+    B200_PDL_SYNC();
+    const int s = blockIdx.y;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    if (sp.qlen <= 0) return;
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (int64_t)channels * nstate) return;
+    const int c = (int)(e / nstate);
+    float* slot = state + (int64_t)state_slots[s] * channels * nstate + e;
+    float carry = (sp.klen - sp.qlen > 0) ? *slot : 0.f;
+    const float a = A[e];
+    const int used = (sp.qlen + chunk_len - 1) / chunk_len;
+    for (int z = 0; z < used; ++z) {
+        float* w = ws_state + ((int64_t)s * nchunks + z) * channels * nstate + e;
+        const float end = *w;
+        *w = carry;
+        carry = fmaf(expf(a * ws_sumdt[((int64_t)s * nchunks + z) * channels + c]), carry, end);
+    }
+    *slot = carry;
 }
 
 }  // namespace
@@ -158,26 +226,49 @@ extern "C" int b200m_causal_conv(const void* x, int64_t x_stride, const void* w,
 extern "C" int b200m_selective_scan(const void* u, const void* dt_raw, const void* dt_bias, const float* A, const void* Bm,
                                     const void* Cm, int64_t bc_stride, const void* Dv, const void* z, int64_t z_stride,
                                     float* state, const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k,
-                                    const int32_t* ctx_lens, void* y, int num_seqs, int channels, int nstate, int is32,
-                                    void* stream) {
+                                    const int32_t* ctx_lens, void* y, int num_seqs, int channels, int nstate, int chunk_len, int max_q,
+                                    float* ws, int is32, void* stream) {
     if (!u || !dt_raw || !dt_bias || !A || !Bm || !Cm || !Dv || !z || !state || !state_slots || !y) return B200_EINVAL;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (channels <= 0 || nstate <= 0) return B200_EINVAL;
     if (nstate > 32 * SCAN_LANES) return B200_EUNSUPPORTED;
     if (num_seqs <= 0) return B200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    dim3 grid((channels + SCAN_CH - 1) / SCAN_CH, num_seqs);
-#define SCAN_GO(N)                                                                                                             \
-    B200M_DISPATCH(is32, B200_LAUNCH((selective_scan_kernel<T, N>), grid, SCAN_LANES * SCAN_CH, 0, st, static_cast<const T*>(u), \
-                                     static_cast<const T*>(dt_raw), static_cast<const T*>(dt_bias), A, static_cast<const T*>(Bm), \
-                                     static_cast<const T*>(Cm), bc_stride, static_cast<const T*>(Dv), static_cast<const T*>(z),  \
-                                     z_stride, state, state_slots, cu_q, cu_k, ctx_lens, static_cast<T*>(y), channels, nstate))
+    const bool chunked = ws != nullptr && chunk_len > 0 && max_q > chunk_len;
+    const int nchunks = chunked ? (max_q + chunk_len - 1) / chunk_len : 1;
+    float* ws_state = ws;
+    float* ws_sumdt = ws ? ws + (int64_t)num_seqs * nchunks * channels * nstate : nullptr;
+    dim3 grid((channels + SCAN_CH - 1) / SCAN_CH, num_seqs, 1);
+#define SCAN_GO(N, MODE)                                                                                                       \
+    B200M_DISPATCH(is32, B200_LAUNCH((selective_scan_kernel<T, N, MODE>), grid, SCAN_LANES * SCAN_CH, 0, st,                    \
+                                     static_cast<const T*>(u), static_cast<const T*>(dt_raw), static_cast<const T*>(dt_bias), A, \
+                                     static_cast<const T*>(Bm), static_cast<const T*>(Cm), bc_stride, static_cast<const T*>(Dv), \
+                                     static_cast<const T*>(z), z_stride, state, state_slots, cu_q, cu_k, ctx_lens,             \
+                                     static_cast<T*>(y), channels, nstate, chunk_len, nchunks, ws_state, ws_sumdt))
+#define SCAN_ALL(MODE)                  \
+    do {                                \
+        if (npl <= 2) SCAN_GO(2, MODE);       \
+        else if (npl <= 4) SCAN_GO(4, MODE);  \
+        else if (npl <= 8) SCAN_GO(8, MODE);  \
+        else if (npl <= 16) SCAN_GO(16, MODE); \
+        else SCAN_GO(32, MODE);               \
+    } while (0)
     const int npl = (nstate + SCAN_LANES - 1) / SCAN_LANES;
-    if (npl <= 2) SCAN_GO(2);
-    else if (npl <= 4) SCAN_GO(4);
-    else if (npl <= 8) SCAN_GO(8);
-    else if (npl <= 16) SCAN_GO(16);
-    else SCAN_GO(32);
+    if (!chunked) {
+        SCAN_ALL(0);
+        return b200_launch_status(nullptr);
+    }
+    grid.z = nchunks;
+    SCAN_ALL(1);
+    int rc = b200_launch_status(nullptr);
+    if (rc != B200_OK) return rc;
+    const int64_t cn = (int64_t)channels * nstate;
+    B200_LAUNCH((scan_carry_kernel), dim3((unsigned)((cn + 255) / 256), num_seqs), 256, 0, st, A, state, state_slots, cu_q, cu_k, ctx_lens,
+                channels, nstate, chunk_len, nchunks, ws_state, (const float*)ws_sumdt);
+    rc = b200_launch_status(nullptr);
+    if (rc != B200_OK) return rc;
+    SCAN_ALL(3);
+#undef SCAN_ALL
 #undef SCAN_GO
     return b200_launch_status(nullptr);
 }

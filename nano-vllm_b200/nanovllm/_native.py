@@ -55,9 +55,9 @@ MIX_SIGNATURES = {
     "b200m_ff_act": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp]),
     "b200m_latent_store": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "b200m_latent_attention": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                    _f, _i, _i, _vp]),
+                                    _f, _i, _i, _i, _vp, _vp]),
     "b200m_causal_conv": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "b200m_selective_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+    "b200m_selective_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i,
                                   _vp]),
     "b200m_moe_tile_rows": (_i, []),
     "b200m_moe_route": (_i, [_vp, _i64, _i, _i, _i, _vp, _vp, _vp]),

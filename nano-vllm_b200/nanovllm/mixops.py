@@ -53,6 +53,15 @@ def _stream() -> int:
     return ops._stream()          # counts the launch too
 
 
+_SMS = [0]
+
+
+def _sm_count() -> int:
+    if not _SMS[0]:
+        _SMS[0] = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _SMS[0]
+
+
 def _call(name, *args):
     nat.check_mix(getattr(nat.load_mix(), name)(*args))
 
@@ -140,14 +149,27 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, c
     _same(is32, q_raw, cache)
     if out is None:
         out = torch.empty_like(q_lat)
+    # single-token steps: few (sequence) CTAs would each walk a whole context; share the key tiles out so that about two
+    # CTAs per SM are in flight.  The bound comes from the block-table width (static, so it also holds inside a CUDA graph).
+    splits, part = 1, None
+    if not is32 and not fma and spans.cu_q is None and H <= 64:
+        tiles = -(-(block_tables.shape[1] * block_size) // 64)
+        chunks = -(-rank // (128 if rank <= 128 else 256))
+        splits = max(1, min(tiles, 32, -(-2 * _sm_count() // max(spans.num_seqs * chunks, 1))))
+        if splits > 1:
+            part = torch.empty(spans.num_seqs * splits * 4 * H * (rank + 2), dtype=torch.float32, device=q_lat.device)   # x4: one partial per warp when H <= 16
+            ops.LAUNCHES[0] += 1
     _call("b200m_latent_attention", q_lat.data_ptr(), q_raw.data_ptr(), q_raw.shape[2], q_rot_off, cache.data_ptr(),
           block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
           sink.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1], out.data_ptr(), n, spans.num_seqs, spans.max_q, H, rank,
-          rot_dim, scale, is32, int(fma), _stream())
+          rot_dim, scale, is32, int(fma), splits, _p(part), _stream())
     return out
 
 
 # ---- selective scan ------------------------------------------------------------------------------------------------------
+SCAN_CHUNK = 64          # tokens per chunk of the chunk-parallel form
+
+
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
                 state_slots: torch.Tensor, spans: StepSpans, out: torch.Tensor | None = None) -> torch.Tensor:
     """x [n, channels] (row-strided view) -> silu(conv(x) + bias) [n, channels]; conv_state [slots, taps - 1, channels] fp32
@@ -178,9 +200,14 @@ def selective_scan(u, dt_raw, dt_bias, A, Bm, Cm, Dv, z, state, state_slots, spa
     _same(is32, dt_raw, dt_bias, Bm, Cm, Dv, z)
     if out is None:
         out = torch.empty_like(u)
+    ws, chunk = None, SCAN_CHUNK
+    if spans.max_q > 2 * chunk:            # long portions: chunks in parallel (three launches) instead of one serial walk
+        nchunks = -(-spans.max_q // chunk)
+        ws = torch.empty(spans.num_seqs * nchunks * channels * (nstate + 1), dtype=torch.float32, device=u.device)
+        ops.LAUNCHES[0] += 2
     _call("b200m_selective_scan", u.data_ptr(), dt_raw.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
           Bm.stride(0), Dv.data_ptr(), z.data_ptr(), z.stride(0), state.data_ptr(), state_slots.data_ptr(), _p(spans.cu_q),
-          _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, channels, nstate, is32, _stream())
+          _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, channels, nstate, chunk, spans.max_q, _p(ws), is32, _stream())
     return out
 
 

@@ -60,8 +60,9 @@ def make_engine(kind: str, size: str, max_seqs: int, max_tokens: int, max_len: i
         hf = SimpleNamespace(**hf_config_dict(dict(hidden_size=width, num_hidden_layers=layers, num_attention_heads=16, num_key_value_heads=8,
                                                    head_dim=128, intermediate_size=3 * width, vocab_size=VOCAB, tie_word_embeddings=False)))
     os.environ["NANOVLLM_ALLOW_RANDOM_INIT"] = "1"
+    blocks = max_seqs * (-(-max_len // 256) + 1)
     cfg = Config("/nonexistent-random-init", hf_config=hf, max_num_seqs=max_seqs, max_num_batched_tokens=max_tokens, max_model_len=max_len,
-                 kvcache_block_size=256, gpu_memory_utilization=0.5)
+                 kvcache_block_size=256, num_kvcache_blocks=blocks)
     Sequence.block_size = 256
     runner = ModelRunner(cfg, 0, None, sample_seed=1)
     return runner, Scheduler(cfg), Sequence
@@ -97,6 +98,8 @@ def throughput(kind: str, size: str, batch: int, prompt: int, new_tokens: int, w
                "prefill_ms": acc[True][0], "decode_ms_per_step": acc[False][0] / max(acc[False][1] // batch, 1)}
     runner.exit()
     del runner, sched
+    import gc
+    gc.collect()
     torch.cuda.empty_cache()
     return res
 
@@ -232,6 +235,7 @@ def main(argv=None):
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--new-tokens", type=int, default=48)
     ap.add_argument("--no-kernels", action="store_true")
+    ap.add_argument("--no-models", action="store_true")
     a = ap.parse_args(argv)
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -242,7 +246,7 @@ def main(argv=None):
     for size in a.sizes.split(","):
         t0 = time.time()
         entry = {"dims": dict(zip(("width", "layers", "heads", "kv_rank", "experts", "top"), SIZES[size]))}
-        for kind in ("tafopel", "qwen3"):
+        for kind in () if a.no_models else ("tafopel", "qwen3"):
             entry[kind] = throughput(kind, size, a.batch, a.prompt, a.new_tokens)
         if not a.no_kernels:
             entry["kernels"] = kernel_table(size, peaks)
