@@ -230,7 +230,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     __nv_bfloat16* Ks = Qs + MMA_BM * DS;
     const int s = blockIdx.y;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
-    const int nrows = sp.qlen * H, row0 = blockIdx.x * MMA_BM;
+    // the last row tiles of a portion see the most keys: they are launched first
+    const int nrows = sp.qlen * H, row0 = (gridDim.x - 1 - blockIdx.x) * MMA_BM;
     if (row0 >= nrows) return;
     // grid.z = (column chunk, key split): with splits > 1 (single-token steps) every CTA covers a contiguous share of the
     // key tiles and leaves unnormalised (acc, max, sum) partials for latent_merge_kernel
@@ -240,31 +241,35 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
 
-    // ---- stage Q (rotating its last rot_dim elements), zero the padding of both tiles ----
-    for (int e = tid; e < MMA_BM * DS; e += 128) {
-        const int r = e / DS, c = e - r * DS;
+    // ---- stage Q (rotating its last rot_dim elements), zero the padding of both tiles: a warp per row, lanes over columns ----
+    for (int r = warp; r < MMA_BM; r += 4) {
         const int rr = row0 + r;
-        __nv_bfloat16 v = zero;
-        if (rr < nrows && c < D) {
-            const int i = rr / H, h = rr - i * H;
-            const int64_t tok = sp.q0 + i;
-            if (c < rank) {
-                v = q_lat[((int64_t)h * total_q + tok) * rank + c];
-            } else {
-                const int cr = c - rank;
-                const __nv_bfloat16* qr = q_raw + (tok * H + h) * q_head_stride + q_rot_off;
-                if (cr < rope_dims) {
-                    const float* cs = cos_sin + (int64_t)(first + i) * rope_dims;
-                    const int half = rope_dims >> 1, p = cr >> 1;
-                    const float u = __bfloat162float(qr[2 * p]), w = __bfloat162float(qr[2 * p + 1]);
-                    v = __float2bfloat16_rn((cr & 1) ? (w * cs[p] + u * cs[half + p]) : (u * cs[p] - w * cs[half + p]));
+        const bool live_row = rr < nrows;
+        const int i = live_row ? rr / H : 0, h = live_row ? rr - i * H : 0;
+        const int64_t tok = sp.q0 + i;
+        const __nv_bfloat16* ql = q_lat + ((int64_t)h * total_q + tok) * rank;
+        const __nv_bfloat16* qr = q_raw + (tok * H + h) * q_head_stride + q_rot_off;
+        const float* cs = cos_sin + (int64_t)(first + i) * rope_dims;
+        const int half = rope_dims >> 1;
+        for (int c = lane; c < DS; c += 32) {
+            __nv_bfloat16 v = zero;
+            if (live_row && c < D) {
+                if (c < rank) {
+                    v = ql[c];
                 } else {
-                    v = qr[cr];
+                    const int cr = c - rank;
+                    if (cr < rope_dims) {
+                        const int p = cr >> 1;
+                        const float u = __bfloat162float(qr[2 * p]), w = __bfloat162float(qr[2 * p + 1]);
+                        v = __float2bfloat16_rn((cr & 1) ? (w * cs[p] + u * cs[half + p]) : (u * cs[p] - w * cs[half + p]));
+                    } else {
+                        v = qr[cr];
+                    }
                 }
             }
+            Qs[r * DS + c] = v;
+            if (c >= Dp) Ks[r * DS + c] = zero;
         }
-        Qs[e] = v;
-        if (c >= Dp) Ks[e] = zero;
     }
     // rows of this warp: g and g + 8 of its 16
     constexpr int NKT = WS ? 2 : 8;                       // 8-key tiles of S per warp
@@ -304,31 +309,23 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     }
     for (int j0 = j_begin; j0 < j_end; j0 += MMA_BN) {
         __syncthreads();
-        // ---- stage 64 cache rows ----
-        if (vec) {
-            const int c8n = Dp >> 3;
-            for (int e = tid; e < MMA_BN * c8n; e += 128) {
-                const int r = e / c8n, c = (e - r * c8n) << 3;
-                const int j = j0 + r;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (j < kmax && c < D) {
-                    const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
-                    v = *reinterpret_cast<const uint4*>(cache + slot * D + c);
+        // ---- stage 64 cache rows: a warp per row (one page lookup), lanes over 16-byte pieces ----
+        for (int r = warp; r < MMA_BN; r += 4) {
+            const int j = j0 + r;
+            const bool in = j < kmax;
+            const __nv_bfloat16* src = cache;
+            if (in) src = cache + ((int64_t)bt[j / block_size] * block_size + (j % block_size)) * D;
+            if (vec) {                                    // asynchronous 16-byte copies (zero-filled outside the row): all in flight at once
+                for (int c = lane << 3; c < Dp; c += 256) {
+                    const bool ok = in && c < D;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_base + (uint32_t)((r * DS + c) * 2)),
+                                 "l"(ok ? (const void*)(src + c) : (const void*)cache), "r"(ok ? 16 : 0) : "memory");
                 }
-                *reinterpret_cast<uint4*>(Ks + r * DS + c) = v;
-            }
-        } else {
-            for (int e = tid; e < MMA_BN * Dp; e += 128) {
-                const int r = e / Dp, c = e - r * Dp;
-                const int j = j0 + r;
-                __nv_bfloat16 v = zero;
-                if (j < kmax && c < D) {
-                    const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
-                    v = cache[slot * D + c];
-                }
-                Ks[r * DS + c] = v;
+            } else {
+                for (int c = lane; c < Dp; c += 32) Ks[r * DS + c] = (in && c < D) ? src[c] : zero;
             }
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
         if (!warp_live || j0 + koff > warp_pos_max) continue;
         // ---- S = Q K^T (16 rows x NKT * 8 keys per warp) ----

@@ -94,6 +94,31 @@ __global__ void ff_act_kernel(const T* __restrict__ x, T* __restrict__ out, int6
     }
 }
 
+// bf16 rows whose halves are multiples of 8: 8 columns per thread, 128-bit accesses, one row per blockIdx.y
+__global__ void __launch_bounds__(256) ff_act_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int n, int kind) {
+    B200_PDL_SYNC();
+    const int c = (blockIdx.x * 256 + threadIdx.x) << 3;
+    if (c >= n) return;
+    const int64_t r = blockIdx.y;
+    float o[8];
+    if (kind == 1) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + r * n + c), v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float t = fmaxf(v[e], 0.f);
+            o[e] = t * t;
+        }
+    } else {
+        float gt[8], up[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + r * 2 * n + c), gt);
+        unpack8(*reinterpret_cast<const uint4*>(x + r * 2 * n + n + c), up);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (kind == 0 ? gelu_tanh_(gt[e]) : siluf_(gt[e])) * up[e];
+    }
+    *reinterpret_cast<uint4*>(out + r * n + c) = pack8(o);
+}
+
 }  // namespace
 
 extern "C" int b200m_abi_version(void) { return 1; }
@@ -129,6 +154,15 @@ extern "C" int b200m_rmsnorm(const void* x, int64_t x_stride, const void* w, voi
 extern "C" int b200m_ff_act(const void* x, void* out, int64_t rows, int n, int kind, int is32, void* stream) {
     if (!x || !out || rows < 0 || n <= 0 || kind < 0 || kind > 2) return B200_EINVAL;
     if (rows == 0) return B200_OK;
+    if (!is32 && n % 8 == 0 && rows <= 65535 * 32 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (int64_t r0 = 0; r0 < rows; r0 += 65535) {             // grid.y limit
+            const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
+            const int64_t in_row = kind == 1 ? n : 2 * (int64_t)n;
+            B200_LAUNCH((ff_act_vec_kernel), dim3((n / 8 + 255) / 256, (unsigned)nr), 256, 0, static_cast<cudaStream_t>(stream),
+                        static_cast<const __nv_bfloat16*>(x) + r0 * in_row, static_cast<__nv_bfloat16*>(out) + r0 * n, n, kind);
+        }
+        return b200_launch_status(nullptr);
+    }
     const int64_t total = rows * n;
     B200M_DISPATCH(is32, B200_LAUNCH((ff_act_kernel<T>), (unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream),
                                      static_cast<const T*>(x), static_cast<T*>(out), rows, n, kind));

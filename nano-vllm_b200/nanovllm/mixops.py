@@ -155,7 +155,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, c
     if not is32 and not fma and spans.cu_q is None and H <= 64:
         tiles = -(-(block_tables.shape[1] * block_size) // 64)
         chunks = -(-rank // (128 if rank <= 128 else 256))
-        splits = max(1, min(tiles, 32, -(-2 * _sm_count() // max(spans.num_seqs * chunks, 1))))
+        splits = max(1, min(tiles, 32, (2 * _sm_count()) // max(spans.num_seqs * chunks, 1)))      # whole waves: never a few CTAs over
         if splits > 1:
             part = torch.empty(spans.num_seqs * splits * 4 * H * (rank + 2), dtype=torch.float32, device=q_lat.device)   # x4: one partial per warp when H <= 16
             ops.LAUNCHES[0] += 1
