@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         for (int n = 0; n < NKT; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
         const uint32_t a_addr = qs_base + (uint32_t)(((rwarp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
         const uint32_t b_addr = ks_base + (uint32_t)(((koff + (lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
+#pragma unroll 2
         for (int kk = 0; kk < Dp; kk += 16) {
             uint32_t a0, a1, a2, a3;
             ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
@@ -390,15 +391,28 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         }
         // ---- O += P V ----
         const uint32_t v_addr = ks_base + (uint32_t)(((koff + (lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
+        if (np_used == NT_O / 2) {                        // the usual case, without predicates: loads run ahead of the products
 #pragma unroll
-        for (int kk = 0; kk < NKT / 2; ++kk) {
+            for (int kk = 0; kk < NKT / 2; ++kk) {
 #pragma unroll
-            for (int np = 0; np < NT_O / 2; ++np) {
-                if (np < np_used) {
+                for (int np = 0; np < NT_O / 2; ++np) {
                     uint32_t b0, b1, b2, b3;
                     ldsm_x4_t(v_addr + (uint32_t)((kk * 16 * DS + np * 16) * 2), b0, b1, b2, b3);
                     mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
                     mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int kk = 0; kk < NKT / 2; ++kk) {
+#pragma unroll
+                for (int np = 0; np < NT_O / 2; ++np) {
+                    if (np < np_used) {
+                        uint32_t b0, b1, b2, b3;
+                        ldsm_x4_t(v_addr + (uint32_t)((kk * 16 * DS + np * 16) * 2), b0, b1, b2, b3);
+                        mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+                        mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+                    }
                 }
             }
         }
