@@ -195,7 +195,7 @@ int launch_attn(const void* q_lat, const void* q_raw, int q_head_stride, int q_r
 // O += P V over their first `rank` columns.  One CTA covers at most MMA_OC output columns (grid.z walks wider latents and
 // recomputes S).  Scores, softmax statistics and O accumulate in fp32 registers; the sink seeds the running maximum and sum.
 // ---------------------------------------------------------------------------------------------------------------------------
-constexpr int MMA_BM = 64, MMA_BN = 64;
+constexpr int MMA_BM = 64;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -216,7 +216,8 @@ __host__ __device__ inline int mma_row_stride(int D) {
 
 // WS (single-token steps with at most 16 heads): the four warps share the 16 query rows and each takes 16 of a tile's 64 keys,
 // leaving one partial per (split, warp).
-template <int NT_O, bool WS>
+// BN: keys per staged tile (64; 32 for wide rows, so that two CTAs still fit in an SM's shared memory).
+template <int NT_O, bool WS, int BN>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_raw, int q_head_stride, int q_rot_off,
     const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
@@ -224,6 +225,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const float* __restrict__ sink, const float* __restrict__ cos_sin, int rope_dims, __nv_bfloat16* __restrict__ out,
     int total_q, int H, int rank, int rot_dim, float scale, int splits, float* __restrict__ part) {
     B200_PDL_SYNC();
+    constexpr int MMA_BN = BN;
+    static_assert(!WS || BN == 64, "the warp-split form shares out 64-key tiles");
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = rank + rot_dim, Dp = (D + 15) & ~15, DS = mma_row_stride(D);
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
@@ -268,11 +271,11 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
                 }
             }
             Qs[r * DS + c] = v;
-            if (c >= Dp) Ks[r * DS + c] = zero;
+            if (c >= Dp && r < MMA_BN) Ks[r * DS + c] = zero;
         }
     }
     // rows of this warp: g and g + 8 of its 16
-    constexpr int NKT = WS ? 2 : 8;                       // 8-key tiles of S per warp
+    constexpr int NKT = WS ? 2 : BN / 8;                  // 8-key tiles of S per warp
     const int rwarp = WS ? 0 : warp;                      // which 16 rows of the tile this warp owns
     const int koff = WS ? warp * 16 : 0;                  // first key of the tile this warp looks at
     float m_run[2], l_run[2];
@@ -474,19 +477,19 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
     }
 }
 
-template <int NT_O, bool WS>
-int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+template <int NT_O, bool WS, int BN>
+int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
                     const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                     const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
                     int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
     const int DS = mma_row_stride(rank + rot_dim);
     if (splits < 1 || max_q != 1 || cu_q != nullptr || part == nullptr || H > MMA_BM) splits = 1;
-    const size_t smem = (size_t)(MMA_BM + MMA_BN) * DS * sizeof(__nv_bfloat16);
-    int rc = ensure_smem(latent_attn_mma_kernel<NT_O, WS>, smem);
+    const size_t smem = (size_t)(MMA_BM + BN) * DS * sizeof(__nv_bfloat16);
+    int rc = ensure_smem(latent_attn_mma_kernel<NT_O, WS, BN>, smem);
     if (rc != B200_OK) return rc;
     dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, ((rank + NT_O * 8 - 1) / (NT_O * 8)) * splits);
     using bf = __nv_bfloat16;
-    B200_LAUNCH((latent_attn_mma_kernel<NT_O, WS>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
+    B200_LAUNCH((latent_attn_mma_kernel<NT_O, WS, BN>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
                 q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
                 sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale, splits, part);
     rc = b200_launch_status(nullptr);
@@ -494,6 +497,22 @@ int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int q_head_stride, 
     B200_LAUNCH((latent_merge_kernel), dim3(num_seqs, H), 128, 0, stream, (const float*)part, ctx_lens, WS ? splits * 4 : splits, H, rank,
                 total_q, static_cast<bf*>(out));
     return b200_launch_status(nullptr);
+}
+
+template <int NT_O, bool WS>
+int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+                       const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
+                       const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
+                       int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+    // 64-key tiles while two CTAs of (64 + 64) staged rows fit in an SM; 32-key tiles for wider rows
+    const bool narrow = !WS && (size_t)(MMA_BM + 64) * mma_row_stride(rank + rot_dim) * sizeof(__nv_bfloat16) > 112 * 1024;
+    if (narrow)
+        return launch_attn_mma_bn<NT_O, false, 32>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
+                                                   splits, part, stream);
+    return launch_attn_mma_bn<NT_O, WS, 64>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                            ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale, splits,
+                                            part, stream);
 }
 
 template <int NT_O>

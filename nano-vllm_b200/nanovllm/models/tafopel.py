@@ -98,6 +98,7 @@ class TafopelForCausalLM:
         self.has_recurrent_state = any(isinstance(b.mixer, SelectiveScanMixer) for b in self.blocks)
         self.block_size = 0
         self._bound = False
+        self._mm_f32_out = True
 
     # ---- weights -----------------------------------------------------------------------------------------------------
     def load_hf_tensor(self, name: str, w: torch.Tensor) -> None:
@@ -232,4 +233,9 @@ class TafopelForCausalLM:
         hn = self.final_norm(hidden, rows_idx=rows)
         if self.dtype == torch.float32:
             return F.linear(hn, self.lm_head)
-        return torch.mm(hn, self.lm_head.t(), out_dtype=torch.float32)
+        if self._mm_f32_out:
+            try:
+                return torch.mm(hn, self.lm_head.t(), out_dtype=torch.float32)        # bf16 operands, fp32 accumulator written as is
+            except (RuntimeError, TypeError):
+                self._mm_f32_out = False          # shapes or a library build without that output type: round once to bf16 instead
+        return F.linear(hn, self.lm_head).float()

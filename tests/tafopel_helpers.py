@@ -56,6 +56,19 @@ def config_b():
                    (latent(heads=5, dim=8, rot_dim=6, vdim=4, kv_rank=136, q_rank=16, scale=0.35), None)], width=48, vocab=61)
 
 
+def config_c():
+    """attention only: two layers read the first layer's cache, mixed feed-forwards."""
+    return config([(latent(heads=4, dim=8, rot_dim=8, vdim=8, kv_rank=24, q_rank=16), moe(4, 2, 16, 0)),
+                   (latent(heads=2, dim=16, rot_dim=8, vdim=12, kv_rank=24, q_rank=8, kv_from=0), None),
+                   (latent(heads=7, dim=8, rot_dim=8, vdim=8, kv_rank=24, q_rank=40, kv_from=0), dense(32))], width=40, vocab=50)
+
+
+def config_d():
+    """selective scan only (no paged cache at all)."""
+    return config([(mamba(inner=56, state=4, dt_rank=2, conv=3), dense(48)), (mamba(inner=32, state=12, dt_rank=4, conv=7), None)],
+                  width=32, vocab=40)
+
+
 def shapes(cfg):
     W, out = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "head": (cfg["vocab"], cfg["width"]), "final.norm": (cfg["width"],)}
     for i, layer in enumerate(cfg["layers"]):

@@ -294,7 +294,7 @@ class Replay:
 def checkpoints(tmp_path_factory):
     root = tmp_path_factory.mktemp("tafopel")
     out = {}
-    for name, cfg in (("a", th.config_a()), ("b", th.config_b())):
+    for name, cfg in (("a", th.config_a()), ("b", th.config_b()), ("c", th.config_c()), ("d", th.config_d())):
         W = th.random_weights(cfg, 21)
         out[name] = (th.write_checkpoint(str(root / name), cfg, W), cfg, W)
     return out
@@ -347,7 +347,7 @@ def test_long_decoding_matches_the_prompt_path(engines, checkpoints, name, dtype
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_portions_of_many_sizes(engines, checkpoints, name, dtype):
     e = engines(name, dtype)
     cuts = (2, 3, 2, 31, 16, 2, 1, 1, 48, 15, 1, 5, 33)
