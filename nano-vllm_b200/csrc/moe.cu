@@ -70,7 +70,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     }
 }
 
-constexpr int MG_BM = 32, MG_BN = 64, MG_BK = 32;
+constexpr int MG_BM = 64, MG_BN = 64, MG_BK = 32;
+constexpr int MG_TM = MG_BM / 16;          // rows per thread of the FMA kernel (16 x 16 threads)
 
 // A rows: src_rows == nullptr -> row i of A itself (the grouped intermediate); else pair = sorted_rows[i], token = pair / top,
 // A row = tokens[token] * wgt[pair] (rounded to T: it is the expert's input tensor).  act: 0 none, 1 relu^2.
@@ -95,8 +96,8 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
         sc[threadIdx.x] = (p >= 0 && gather) ? wgt[p] : 1.0f;
     }
     __syncthreads();
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 2 rows x 4 columns each
-    float acc[2][4] = {};
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, MG_TM rows x 4 columns each
+    float acc[MG_TM][4] = {};
     for (int k0 = 0; k0 < K; k0 += MG_BK) {
         for (int i = threadIdx.x; i < MG_BM * MG_BK; i += 256) {
             const int r = i / MG_BK, k = i % MG_BK;
@@ -114,19 +115,21 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
         __syncthreads();
 #pragma unroll 8
         for (int k = 0; k < MG_BK; ++k) {
-            const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+            float av[MG_TM];
+#pragma unroll
+            for (int r = 0; r < MG_TM; ++r) av[r] = As[ty * MG_TM + r][k];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float w = Ws[tx + 16 * j][k];
-                acc[0][j] = fmaf(a0, w, acc[0][j]);
-                acc[1][j] = fmaf(a1, w, acc[1][j]);
+#pragma unroll
+                for (int r = 0; r < MG_TM; ++r) acc[r][j] = fmaf(av[r], w, acc[r][j]);
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = ty * 2 + r;
+    for (int r = 0; r < MG_TM; ++r) {
+        const int row = ty * MG_TM + r;
         if (src[row] < 0) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -143,7 +146,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// Tensor-core form of the grouped GEMM (bf16): one 32-row tile of one expert x 128 output columns per CTA, K in steps of 64
+// Tensor-core form of the grouped GEMM (bf16): one 64-row tile of one expert x 128 output columns per CTA (8 warps, 32 x 32 each), K in steps of 64
 // through a two-stage shared-memory ring (weights by cp.async, the gathered / weighted input rows through registers),
 // mma.sync m16n8k16 with fp32 accumulation.  Needs K % 8 == 0 and 16-byte aligned rows; other shapes take the FMA kernel.
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -165,7 +168,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t a_stride,
+__global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t a_stride,
                                                            const int32_t* __restrict__ sorted_rows, const float* __restrict__ wgt, int top,
                                                            bool gather, const int32_t* __restrict__ tile_expert,
                                                            const int32_t* __restrict__ num_tiles, const __nv_bfloat16* __restrict__ W, int N,
@@ -173,14 +176,18 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
     B200_PDL_SYNC();
     const int tile = blockIdx.y;
     if (tile >= num_tiles[0]) return;
-    __shared__ __align__(16) __nv_bfloat16 As[2][MG_BM][MM_LD];
-    __shared__ __align__(16) __nv_bfloat16 Bs[2][MM_BN][MM_LD];
+    extern __shared__ __align__(16) unsigned char mm_smem[];
+    typedef __nv_bfloat16 (*ATile)[MG_BM][MM_LD];
+    typedef __nv_bfloat16 (*BTile)[MM_BN][MM_LD];
+    ATile As = reinterpret_cast<ATile>(mm_smem);                                                  // [2][MG_BM][MM_LD]
+    BTile Bs = reinterpret_cast<BTile>(mm_smem + 2 * MG_BM * MM_LD * sizeof(__nv_bfloat16));      // [2][MM_BN][MM_LD]
     __shared__ int src[MG_BM];
     __shared__ float sc[MG_BM];
     const int e = tile_expert[tile];
     const __nv_bfloat16* We = W + (int64_t)e * N * K;
     const int row0 = tile * MG_BM, col0 = blockIdx.x * MM_BN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wr = warp >> 2, wc = warp & 3;                            // this warp's 32 rows and 32 columns of the tile
     if (tid < MG_BM) {
         const int p = sorted_rows[row0 + tid];
         src[tid] = p < 0 ? -1 : (gather ? p / top : row0 + tid);
@@ -188,12 +195,12 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
     }
     __syncthreads();
     auto load_stage = [&](int st, int k0) {
-        for (int i = tid; i < MM_BN * (MM_BK / 8); i += 128) {          // weights: 128 rows x 8 chunks of 16 bytes
+        for (int i = tid; i < MM_BN * (MM_BK / 8); i += 256) {          // weights: 128 rows x 8 chunks of 16 bytes
             const int r = i >> 3, c = (i & 7) << 3;
             const bool ok = col0 + r < N && k0 + c < K;
             cp_async16(smem_u32(&Bs[st][r][c]), ok ? (const void*)(We + (int64_t)(col0 + r) * K + k0 + c) : (const void*)We, ok ? 16 : 0);
         }
-        for (int i = tid; i < MG_BM * (MM_BK / 8); i += 128) {          // input rows: gathered, weighted, rounded
+        for (int i = tid; i < MG_BM * (MM_BK / 8); i += 256) {          // input rows: gathered, weighted, rounded
             const int r = i >> 3, c = (i & 7) << 3;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (src[r] >= 0 && k0 + c < K) {
@@ -226,8 +233,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
             cp_async_wait<0>();
         }
         __syncthreads();
-        const uint32_t a_base = smem_u32(&As[st][lane & 15][(lane >> 4) << 3]);
-        const uint32_t b_base = smem_u32(&Bs[st][warp * 32 + (lane & 7) + ((lane >> 4) << 3)][((lane >> 3) & 1) << 3]);
+        const uint32_t a_base = smem_u32(&As[st][wr * 32 + (lane & 15)][(lane >> 4) << 3]);
+        const uint32_t b_base = smem_u32(&Bs[st][wc * 32 + (lane & 7) + ((lane >> 4) << 3)][((lane >> 3) & 1) << 3]);
 #pragma unroll
         for (int kk = 0; kk < MM_BK; kk += 16) {
             uint32_t a[2][4];
@@ -251,13 +258,13 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-            const int row = mt * 16 + g + 8 * hh;
+            const int row = wr * 32 + mt * 16 + g + 8 * hh;
             if (src[row] < 0) continue;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
-                    const int col = col0 + warp * 32 + nt * 8 + 2 * t4 + q;
+                    const int col = col0 + wc * 32 + nt * 8 + 2 * t4 + q;
                     if (col >= N) continue;
                     float v = acc[mt][nt][2 * hh + q];
                     if (act == 1) {
@@ -317,11 +324,18 @@ extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* so
     if (tc) {
         dim3 g2((N + MM_BN - 1) / MM_BN, max_tiles);
         using bf = __nv_bfloat16;
+        const size_t smem = 2 * (size_t)(MG_BM + MM_BN) * MM_LD * sizeof(bf);
+        cudaError_t ce = out_f32 ? cudaFuncSetAttribute(moe_gemm_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                 : cudaFuncSetAttribute(moe_gemm_mma_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) {
+            b200_tls_cuda_error() = cudaGetErrorString(ce);
+            return B200_ECUDA;
+        }
         if (out_f32)
-            B200_LAUNCH((moe_gemm_mma_kernel<float>), g2, 128, 0, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
+            B200_LAUNCH((moe_gemm_mma_kernel<float>), g2, 256, smem, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
                         tile_expert, num_tiles, static_cast<const bf*>(W), N, K, static_cast<float*>(C), act);
         else
-            B200_LAUNCH((moe_gemm_mma_kernel<bf>), g2, 128, 0, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
+            B200_LAUNCH((moe_gemm_mma_kernel<bf>), g2, 256, smem, st, static_cast<const bf*>(A), a_stride, sorted_rows, wgt, top, gather != 0,
                         tile_expert, num_tiles, static_cast<const bf*>(W), N, K, static_cast<bf*>(C), act);
         return b200_launch_status(nullptr);
     }
