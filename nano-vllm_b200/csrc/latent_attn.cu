@@ -301,6 +301,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int kmax = first + i_hi + 1;
     const int warp_pos_max = first + min(sp.qlen - 1, (row0 + rwarp * 16 + 15) / H);
     const bool warp_live = row0 + rwarp * 16 < nrows;
+    // smallest position among this warp's live rows (a dead row sees nothing, so the masked path handles warps that have one)
+    const int warp_pos_min = (row0 + rwarp * 16 + 15 < nrows) ? first + (row0 + rwarp * 16) / H : -1;
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
     const uint32_t qs_base = smem_u32(Qs), ks_base = smem_u32(Ks);
     const bool vec = (D & 7) == 0;
@@ -313,11 +315,15 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     for (int j0 = j_begin; j0 < j_end; j0 += MMA_BN) {
         __syncthreads();
         // ---- stage 64 cache rows: a warp per row (one page lookup), lanes over 16-byte pieces ----
+        // a tile that lies inside one page (pages are multiples of the tile, tiles start at multiples of it) needs one lookup
+        const bool one_page = (block_size % MMA_BN) == 0;
+        const __nv_bfloat16* page0 = cache;
+        if (one_page) page0 = cache + ((int64_t)bt[j0 / block_size] * block_size + (j0 % block_size)) * D;
         for (int r = warp; r < MMA_BN; r += 4) {
             const int j = j0 + r;
             const bool in = j < kmax;
             const __nv_bfloat16* src = cache;
-            if (in) src = cache + ((int64_t)bt[j / block_size] * block_size + (j % block_size)) * D;
+            if (in) src = one_page ? page0 + (int64_t)r * D : cache + ((int64_t)bt[j / block_size] * block_size + (j % block_size)) * D;
             if (vec) {                                    // asynchronous 16-byte copies (zero-filled outside the row): all in flight at once
                 for (int c = lane << 3; c < Dp; c += 256) {
                     const bool ok = in && c < D;
@@ -337,7 +343,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         for (int n = 0; n < NKT; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
         const uint32_t a_addr = qs_base + (uint32_t)(((rwarp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
         const uint32_t b_addr = ks_base + (uint32_t)(((koff + (lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
-#pragma unroll 2
+#pragma unroll 4
         for (int kk = 0; kk < Dp; kk += 16) {
             uint32_t a0, a1, a2, a3;
             ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
@@ -351,16 +357,28 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         }
         // ---- mask, online softmax ----
         float mx[2] = {m_run[0], m_run[1]};
+        // tiles wholly behind every row of this warp (the bulk of a long portion) need no mask
+        const bool all_visible = j0 + koff + NKT * 8 - 1 <= warp_pos_min;
+        if (all_visible) {
 #pragma unroll
-        for (int n = 0; n < NKT; ++n)
+            for (int n = 0; n < NKT; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = j0 + koff + n * 8 + 2 * t4 + (e & 1);
-                const int k = e >> 1;
-                const float v = (key <= pos_row[k]) ? sc[n][e] * scale : -INFINITY;
-                sc[n][e] = v;
-                mx[k] = fmaxf(mx[k], v);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    sc[n][e] *= scale;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sc[n][e]);
+                }
+        } else {
+#pragma unroll
+            for (int n = 0; n < NKT; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + koff + n * 8 + 2 * t4 + (e & 1);
+                    const int k = e >> 1;
+                    const float v = (key <= pos_row[k]) ? sc[n][e] * scale : -INFINITY;
+                    sc[n][e] = v;
+                    mx[k] = fmaxf(mx[k], v);
+                }
+        }
         float alpha[2], psum[2] = {0.f, 0.f};
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
@@ -385,12 +403,14 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             psum[k] += __shfl_xor_sync(0xffffffffu, psum[k], 2);
             l_run[k] = l_run[k] * alpha[k] + psum[k];
         }
+        if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {      // the running maxima settle early in a long row
 #pragma unroll
-        for (int n = 0; n < NT_O; ++n) {
-            o[n][0] *= alpha[0];
-            o[n][1] *= alpha[0];
-            o[n][2] *= alpha[1];
-            o[n][3] *= alpha[1];
+            for (int n = 0; n < NT_O; ++n) {
+                o[n][0] *= alpha[0];
+                o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1];
+                o[n][3] *= alpha[1];
+            }
         }
         // ---- O += P V ----
         const uint32_t v_addr = ks_base + (uint32_t)(((koff + (lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);

@@ -68,13 +68,14 @@ def identity_rotation(max_pos, dims):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_kernel_finds_one_far_key_and_respects_edges(dtype):
+@pytest.mark.parametrize("bs", [16, 64])
+def test_attention_kernel_finds_one_far_key_and_respects_edges(dtype, bs):
     """One key is made to dominate (its row is a large multiple of the query): the output must be that key's latent when the key
     is visible, and must not move when it is one position too far.  The key sits at page borders, at position 0, and hundreds
     of tokens back; queries are rows of a portion and single decoded tokens, over pages in a scrambled order that also hold a
     stale dominating row just past the sequence's end."""
     from nanovllm import mixops
-    H, rank, rd, bs, L = 3, 40, 8, 16, 420
+    H, rank, rd, L = 3, 40, 8, 420
     D = rank + rd
     g = torch.Generator().manual_seed(7)
     pages = torch.randperm(40, generator=g)[: (L + bs - 1) // bs + 1].to(torch.int32)
@@ -390,6 +391,20 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(engines, check
     assert ended == set(T)
     for k in T:
         assert rel_err(torch.cat(got[k]), oracle_logits(checkpoints, name, T[k])) < TOL[dtype], k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_of_64_tokens(checkpoints, dtype):
+    """Pages as long as the attention kernel's key tile (one page lookup per tile), a prompt in portions and decoding over a page border."""
+    e = Replay(checkpoints["a"][0], dtype, pool_tokens=512, block=64, seqs=2)
+    toks = th.tokens(200, checkpoints["a"][1]["vocab"], 77)
+    got, at = [], 0
+    for n in (70, 58, 1, 1, 1, 60, 9):
+        got.append(e.step([("p", toks[at:at + n])])["p"])
+        at += n
+    e.end("p")
+    e.runner.exit()
+    assert rel_err(torch.cat(got), oracle_logits(checkpoints, "a", toks)) < TOL[dtype]
 
 
 def test_batch_does_not_change_a_request_beyond_rounding(engines, checkpoints):
