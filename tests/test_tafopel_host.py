@@ -157,3 +157,22 @@ def test_plain_implementation_is_causal_and_its_scan_matches_a_closed_form():
         S = torch.exp(-dt) * S + dt * u * u
         want.append(S * u * torch.nn.functional.silu(one(1.0)))
     assert torch.allclose(got, torch.stack(want), atol=1e-12)
+
+
+def test_mixer_library_header_and_binding_agree():
+    """Every entry point include/b200_mixers.h declares is typed in the ctypes table (and exported, when the library is built)."""
+    import ctypes
+    import re
+    from nanovllm import _native as nat
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", "b200_mixers.h")).read(), flags=re.S)
+    names = sorted(set(re.findall(r"\b(b200m_[a-z0-9_]+)\s*\(", text)))
+    assert len(names) >= 14 and set(names) == set(nat.MIX_SIGNATURES)
+    for n in names:                      # argument counts of the prototypes match the table
+        proto = re.search(r"\b%s\s*\(([^;]*?)\)\s*;" % n, text, flags=re.S).group(1).strip()
+        argc = 0 if proto in ("", "void") else proto.count(",") + 1
+        assert argc == len(nat.MIX_SIGNATURES[n][1]), n
+    if nat.mix_lib_path().exists():
+        lib = ctypes.CDLL(str(nat.mix_lib_path()))
+        for n in names:
+            assert hasattr(lib, n), n
