@@ -69,6 +69,15 @@ def config_d():
                   width=32, vocab=40)
 
 
+def config_e():
+    """sizes nearer a small real model: a 192-wide latent (two column passes of the tensor-core kernel), 12 and 5 heads, a 64-wide
+    recurrent state (several lanes per channel), 64 experts of which 6 are used, top == experts."""
+    return config([(latent(heads=12, dim=32, rot_dim=16, vdim=48, kv_rank=192, q_rank=96, scale=0.15), dense(256)),
+                   (mamba(inner=200, state=64, dt_rank=20, conv=4), moe(experts=64, top=6, ff=32, shared=64)),
+                   (latent(heads=5, dim=64, rot_dim=16, vdim=32, kv_rank=192, q_rank=48, kv_from=0, scale=0.11), None),
+                   (mamba(inner=384, state=24, dt_rank=8, conv=2), moe(experts=8, top=8, ff=64, shared=0))], width=160, vocab=300, eps=1e-6)
+
+
 def shapes(cfg):
     W, out = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "head": (cfg["vocab"], cfg["width"]), "final.norm": (cfg["width"],)}
     for i, layer in enumerate(cfg["layers"]):
