@@ -215,7 +215,8 @@ __host__ __device__ inline int mma_row_stride(int D) {
 }
 
 // WS (single-token steps with at most 16 heads): the four warps share the 16 query rows and each takes 16 of a tile's 64 keys,
-// leaving one partial per (split, warp).
+// leaving one partial per (split, warp).  Only those 16 query rows are staged, and the room that saves holds a second key
+// tile: the next tile's asynchronous copies are in flight while the current one is multiplied.
 // BN: keys per staged tile (64; 32 for wide rows, so that two CTAs still fit in an SM's shared memory).
 template <int NT_O, bool WS, int BN>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
@@ -229,8 +230,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     static_assert(!WS || BN == 64, "the warp-split form shares out 64-key tiles");
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = rank + rot_dim, Dp = (D + 15) & ~15, DS = mma_row_stride(D);
+    constexpr int QR = WS ? 16 : MMA_BM;                  // staged query rows
+    constexpr int NBUF = WS ? 2 : 1;                      // staged key tiles
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
-    __nv_bfloat16* Ks = Qs + MMA_BM * DS;
+    __nv_bfloat16* Ks = Qs + QR * DS;
     const int s = blockIdx.y;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     // the last row tiles of a portion see the most keys: they are launched first
@@ -245,7 +248,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
 
     // ---- stage Q (rotating its last rot_dim elements), zero the padding of both tiles: a warp per row, lanes over columns ----
-    for (int r = warp; r < MMA_BM; r += 4) {
+    for (int r = warp; r < QR; r += 4) {
         const int rr = row0 + r;
         const bool live_row = rr < nrows;
         const int i = live_row ? rr / H : 0, h = live_row ? rr - i * H : 0;
@@ -271,9 +274,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
                 }
             }
             Qs[r * DS + c] = v;
-            if (c >= Dp && r < MMA_BN) Ks[r * DS + c] = zero;
         }
     }
+    for (int r = warp; r < NBUF * MMA_BN; r += 4)
+        for (int c = Dp + lane; c < DS; c += 32) Ks[r * DS + c] = zero;
     // rows of this warp: g and g + 8 of its 16
     constexpr int NKT = WS ? 2 : BN / 8;                  // 8-key tiles of S per warp
     const int rwarp = WS ? 0 : warp;                      // which 16 rows of the tile this warp owns
@@ -312,11 +316,12 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         j_begin = split * per * MMA_BN;
         j_end = min(kmax, (split + 1) * per * MMA_BN);
     }
-    for (int j0 = j_begin; j0 < j_end; j0 += MMA_BN) {
-        __syncthreads();
-        // ---- stage 64 cache rows: a warp per row (one page lookup), lanes over 16-byte pieces ----
-        // a tile that lies inside one page (pages are multiples of the tile, tiles start at multiples of it) needs one lookup
-        const bool one_page = (block_size % MMA_BN) == 0;
+    // ---- stage one tile of cache rows: a warp per row (one page lookup), lanes over 16-byte pieces ----
+    // a tile that lies inside one page (pages are multiples of the tile, tiles start at multiples of it) needs one lookup
+    const bool one_page = (block_size % MMA_BN) == 0;
+    auto stage = [&](int j0, int buf) {
+        __nv_bfloat16* Kb = Ks + buf * MMA_BN * DS;
+        const uint32_t kb = ks_base + (uint32_t)(buf * MMA_BN * DS * 2);
         const __nv_bfloat16* page0 = cache;
         if (one_page) page0 = cache + ((int64_t)bt[j0 / block_size] * block_size + (j0 % block_size)) * D;
         for (int r = warp; r < MMA_BN; r += 4) {
@@ -327,22 +332,45 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             if (vec) {                                    // asynchronous 16-byte copies (zero-filled outside the row): all in flight at once
                 for (int c = lane << 3; c < Dp; c += 256) {
                     const bool ok = in && c < D;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_base + (uint32_t)((r * DS + c) * 2)),
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kb + (uint32_t)((r * DS + c) * 2)),
                                  "l"(ok ? (const void*)(src + c) : (const void*)cache), "r"(ok ? 16 : 0) : "memory");
                 }
             } else {
-                for (int c = lane; c < Dp; c += 32) Ks[r * DS + c] = (in && c < D) ? src[c] : zero;
+                for (int c = lane; c < Dp; c += 32) Kb[r * DS + c] = (in && c < D) ? src[c] : zero;
             }
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
+    };
+    const bool pipelined = NBUF == 2 && vec;              // rows that are not whole 16-byte pieces are staged by plain stores, one tile at a time
+    if (pipelined && j_begin < j_end) {
+        stage(j_begin, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    int it = 0;
+    for (int j0 = j_begin; j0 < j_end; j0 += MMA_BN, ++it) {
+        int buf = 0;
+        __syncthreads();                                  // the tile of the last iteration is consumed (and Q is written)
+        if (pipelined) {
+            buf = it & 1;
+            if (j0 + MMA_BN < j_end) {                    // the next tile goes into the other buffer while this one is used
+                stage(j0 + MMA_BN, buf ^ 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+        } else {
+            stage(j0, 0);
+            asm volatile("cp.async.wait_all;" ::: "memory");
+        }
         __syncthreads();
+        const uint32_t kt_base = ks_base + (uint32_t)(buf * MMA_BN * DS * 2);
         if (!warp_live || j0 + koff > warp_pos_max) continue;
         // ---- S = Q K^T (16 rows x NKT * 8 keys per warp) ----
         float sc[NKT][4];
 #pragma unroll
         for (int n = 0; n < NKT; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
         const uint32_t a_addr = qs_base + (uint32_t)(((rwarp * 16 + (lane & 15)) * DS + ((lane >> 4) << 3)) * 2);
-        const uint32_t b_addr = ks_base + (uint32_t)(((koff + (lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
+        const uint32_t b_addr = kt_base + (uint32_t)(((koff + (lane & 7) + ((lane >> 4) << 3)) * DS + (((lane >> 3) & 1) << 3)) * 2);
 #pragma unroll 4
         for (int kk = 0; kk < Dp; kk += 16) {
             uint32_t a0, a1, a2, a3;
@@ -413,7 +441,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
             }
         }
         // ---- O += P V ----
-        const uint32_t v_addr = ks_base + (uint32_t)(((koff + (lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
+        const uint32_t v_addr = kt_base + (uint32_t)(((koff + (lane & 7) + (((lane >> 3) & 1) << 3)) * DS + rc0 + ((lane >> 4) << 3)) * 2);
         if (np_used == NT_O / 2) {                        // the usual case, without predicates: loads run ahead of the products
 #pragma unroll
             for (int kk = 0; kk < NKT / 2; ++kk) {
@@ -504,7 +532,7 @@ int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int q_head_stride, 
                     int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
     const int DS = mma_row_stride(rank + rot_dim);
     if (splits < 1 || max_q != 1 || cu_q != nullptr || part == nullptr || H > MMA_BM) splits = 1;
-    const size_t smem = (size_t)(MMA_BM + BN) * DS * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(WS ? 16 + 2 * BN : MMA_BM + BN) * DS * sizeof(__nv_bfloat16);       // as the kernel lays it out
     int rc = ensure_smem(latent_attn_mma_kernel<NT_O, WS, BN>, smem);
     if (rc != B200_OK) return rc;
     dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, ((rank + NT_O * 8 - 1) / (NT_O * 8)) * splits);
