@@ -3,7 +3,7 @@ its own LLM / flash-attn 2.8.3 / Triton / torch.compile / CUDA-graph path, on th
 
     python baseline/run_reference_gpu.py [passes]
 
-This is the "kernel to beat on the same box" of BASELINE.md section 4 -- context for the headline number, not
+This is the "kernel to beat on the same box" -- context for the headline number, not
 the driver's `--impl reference` arm (that one is the CPU port, as the task tier prescribes).
 Prints one JSON line: {"impl": "reference-gpu", "value": tokens/s, ...}.
 """

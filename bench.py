@@ -504,7 +504,7 @@ def run_b200_arm(args):
                       "e2e_is": "tokens / CUDA-event time around LLM.generate() with host prompts (H2D metadata + D2H tokens every engine step)",
                       "l2": "KV read per decode step (>= 0.5 GB/layer at batch 256) and weights (1.2 GB) exceed the 126 MB L2; "
                             "no flush between passes needed, token values differ per pass (no prefix-cache reuse)",
-                      "vs_baseline_basis": "value (device-busy) / BASELINE.md's 1434.13 tok/s (reference README, RTX 4070 Laptop: "
+                      "vs_baseline_basis": "value (device-busy) / the reference's published 1434.13 tok/s (reference README, RTX 4070 Laptop: "
                                            "the only published number, a wall-clock figure); the like-for-like wall-clock ratio is "
                                            "e2e_vs_baseline",
                       "e2e_vs_baseline": e2e / README_TOK_S,

@@ -3,9 +3,8 @@
  * drops in behind nano-vLLM's attention operator and the small fused ops around it.
  *
  * Every entry point cites the reference interface (GeeeekExplorer/nano-vllm @ bb823b3e) it
- * replaces.  The reference has no FFI layer of its own: its seams are Python-level
- * (SURVEY.md section 8b), so this header is the binding a maintainer would load with ctypes
- * (see INTEGRATION.md).
+ * replaces.  The reference has no FFI layer of its own (its seams are Python-level),
+ * so this header is the binding a maintainer would load with ctypes.
  *
  * Conventions
  *   - returns 0 on success, a negative B200_E* code otherwise (b200_strerror names it);
@@ -211,7 +210,7 @@ int b200_sample(const void* logits, int logits_is_fp32, int64_t logits_stride0,
                 uint64_t seed, uint64_t step, const int64_t* step_dev, int64_t* out,
                 int64_t* out_keys, void* stream);
 
-/* ---- decode-size projections on tcgen05 (validated on a B200 in round 2: tests/test_gpu_linear.py) ----------------
+/* ---- decode-size projections on tcgen05 (validated on a B200: tests/test_gpu_linear.py) ----------------
  *
  * F.linear of the reference's *ParallelLinear layers (layers/linear.py:51,73,153) for small batches, on tcgen05,
  * with what follows fused in (csrc/linear_tc.cu):

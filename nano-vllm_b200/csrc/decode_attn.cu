@@ -4,7 +4,7 @@
 // flash_attn_with_kvcache over paged K/V).  HBM-bandwidth bound: every K/V byte of every live
 // context token is read exactly once per layer per step.
 //
-// Design (DESIGN.md "decode kernel"):
+// Design:
 //   * one persistent launch, one CTA per SM, NWARPS independent warps per CTA;
 //   * the step's work is the list of 16-token chunks ordered by (sequence, kv head, chunk);
 //     it is cut into equal contiguous ranges, one per warp ("stream-K" over KV pages), so the

@@ -1,5 +1,5 @@
 // Single-token paged decode attention, tensor-core formulation (same contract and same stream-K work
-// partition as decode_attn.cu; see that file and DESIGN.md for the scheduling).
+// partition as decode_attn.cu; see that file for the scheduling).
 //
 // What differs is how a warp digests one 16-token chunk:
 //   * K and V chunks arrive as 128-byte-swizzled TMA tensor boxes (cp.async.bulk.tensor.2d over a

@@ -1,6 +1,6 @@
 // The small bandwidth-bound ops around the attention operator, hand-written for sm_100a.
-// They replace the reference's Triton KV scatter and its five @torch.compile sites (SURVEY.md 2b,
-// K1 and K5-K8): fp32 math, one rounding at every stored output (what Inductor generates on a
+// They replace the reference's Triton KV scatter and its five @torch.compile sites:
+// fp32 math, one rounding at every stored output (what Inductor generates on a
 // GPU), 128-bit coalesced global accesses, warp-shuffle reductions.
 #include <cstdlib>
 

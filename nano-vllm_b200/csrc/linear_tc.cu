@@ -1,6 +1,6 @@
 // Small-batch linear layers y = x W^T on the 5th-generation tensor cores, with the op that follows fused in.
 //
-// STATUS: validated on a B200 in round 2 (tests/test_gpu_linear.py, profiles/r02_linear_microbench.json).  On the product
+// STATUS: validated on a B200 (tests/test_gpu_linear.py, profiles/r02_linear_microbench.json).  On the product
 // path for o_proj / down_proj of decode batches <= 128 rows (split-K) and for all four projections of the two-stream decode
 // step (models/qwen3.py::_forward_dual), where a shallow ring lets these CTAs share an SM with the attention kernel.
 //

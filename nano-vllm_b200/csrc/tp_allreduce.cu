@@ -155,7 +155,7 @@ extern "C" int b200_allreduce_add_rmsnorm(const void* peer_bases_dev, uint64_t d
     return b200_launch_status(nullptr);
 }
 
-// Same exchange with the reduction done inside the NVSwitch (default from 4 ranks; validated at 2, 4 and 8 ranks in round 2).  `multicast_base` is the
+// Same exchange with the reduction done inside the NVSwitch (default from 4 ranks; validated at 2, 4 and 8 ranks).  `multicast_base` is the
 // multicast mapping of the same symmetric allocation (torch symmetric memory: handle.multicast_ptr).
 extern "C" int b200_allreduce_add_rmsnorm_nvls(const void* peer_bases_dev, const void* multicast_base, uint64_t data_offset,
                                                uint64_t flag_offset, int* epoch, unsigned int* done, int* err_flag, int rank,

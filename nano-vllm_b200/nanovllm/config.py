@@ -1,7 +1,7 @@
 """Engine configuration (reference nanovllm/config.py:6-25): same fields, same defaults.
 
 Differences, both widenings: ``kvcache_block_size`` may be any power of two in [16, 256]
-(the reference's ``% 256`` assertion exists only for flash-attn's paged path, SURVEY.md S2), and
+(the reference's ``% 256`` assertion exists only for flash-attn's paged path), and
 ``hf_config`` may be supplied pre-built (tests) instead of being read from ``model``.
 """
 from __future__ import annotations

@@ -5,7 +5,7 @@ Same contract as the reference's ModelRunner (nanovllm/engine/model_runner.py:15
 is_prefill) -> list[int]`` returns one token id per sequence; one process per GPU, one thread,
 everything on the current stream, one device->host sync per step.
 
-B200-first differences (DESIGN.md "runner"):
+B200-first differences:
 * per-step metadata travels in ONE pinned staging buffer (two of them, ping-pong, so step N+1 can be staged
   while step N runs) and ONE host->device copy into static device buffers (the reference builds seven pinned
   tensors and seven copies per step);
@@ -442,7 +442,7 @@ class ModelRunner:
         hidden = self.model(input_ids, positions)
         if self.fused_lm_head and rows <= self.g_keyws.numel():
             # opt-in (B200_LM_HEAD=fused): LM head + sampling in one tensor-core kernel, logits never written; parity-green but
-            # slower than the library GEMM + sample_kernel pair (DESIGN.md 3.4), hence not the default
+            # slower than the library GEMM + sample_kernel pair, hence not the default
             last = self.model.last_token_rows(hidden)
             if self.world_size == 1:
                 ops.lm_head_sample(last, self.model.lm_head, temps, self.sample_seed, 0, self.g_keyws, out=self.g_tokens[:rows],

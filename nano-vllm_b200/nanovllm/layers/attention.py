@@ -5,7 +5,7 @@ attributes ``k_cache`` / ``v_cache`` (discovered with ``hasattr`` by the runner,
 engine/model_runner.py:117-121), ``forward(q, k, v) -> o`` reading the process-global Context.
 
 What differs is what the cache tensors look like: a layer's ``k_cache`` is the physical
-page array ``[num_blocks, num_kv_heads, block_size, head_dim]`` (head-major pages, DESIGN.md), bound
+page array ``[num_blocks, num_kv_heads, block_size, head_dim]`` (head-major pages), bound
 to the library once by the runner; block ids and slot numbers mean exactly what they mean in the
 reference.
 """

@@ -35,7 +35,7 @@ def _need(t: torch.Tensor, dtype, name: str):
 
 # ---- KV cache ---------------------------------------------------------------
 def kv_cache_shape(layers, num_blocks, num_kv_heads, block_size, head_dim):
-    """Physical layout (DESIGN.md): [2, layers, blocks, kv_heads, block_size, head_dim]."""
+    """Physical layout: [2, layers, blocks, kv_heads, block_size, head_dim]."""
     return (2, layers, num_blocks, num_kv_heads, block_size, head_dim)
 
 

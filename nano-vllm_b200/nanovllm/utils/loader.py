@@ -3,7 +3,7 @@ model directory is handed to the model, which slices its own tensor-parallel sha
 
 Unlike the reference, a directory without weights is an error unless ``allow_random`` is set, in
 which case the model is filled from a seeded generator (the reference would silently run on
-``torch.empty`` garbage, SURVEY.md S4).
+``torch.empty`` garbage).
 """
 from __future__ import annotations
 

@@ -1,7 +1,7 @@
 """Random-init Qwen3 checkpoints for benchmarking and tests (no network, no real weights here).
 
 Writes what ``Config`` / ``LLMEngine`` / the loader read from a model directory (the same three
-things the reference reads, SURVEY.md appendix A): ``config.json``, a WordLevel ``tokenizer.json``
+things the reference reads): ``config.json``, a WordLevel ``tokenizer.json``
 covering the whole vocabulary, and ``model.safetensors`` with HF parameter names.  Weights are
 N(0, init_std) from a seeded CPU generator, norm weights 1 + 0.1 N(0, 1); the same file is loaded
 by the product, by the CPU oracle and (when present) by the reference itself, so all three see

@@ -182,7 +182,7 @@ def import_reference():
 
 
 def reference_meta_builder(torch, block_size):
-    """The reference's own prepare_* run unbound with a stub self (SURVEY.md section 4)."""
+    """The reference's own prepare_* run unbound with a stub self."""
     from nanovllm.engine.model_runner import ModelRunner
     from nanovllm.utils.context import get_context
     real_tensor = torch.tensor
@@ -292,7 +292,7 @@ def gen_hash_kat():
     for n, prefix in ((256, -1), (256, 12345), (16, -1), (16, 2**63 + 5), (1, -1), (33, 987654321987654321)):
         toks = list(range(n)) if not cases else [rnd.randint(0, 151935) for _ in range(n)]
         cases.append(dict(tokens=toks, prefix=prefix, hash=BlockManager.compute_hash(toks, prefix)))
-    assert cases[0]["hash"] == 5218229187174952702
+    assert cases[0]["hash"] == 5218229187174952702          # hash of range(256) under the reference's own function
     with open(os.path.join(GOLD, "hash_kat.json"), "w") as f:
         json.dump(cases, f)
     print("hash KATs:", len(cases))

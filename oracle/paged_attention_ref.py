@@ -15,7 +15,7 @@ Follows, function by function:
 
 Logical cache layout here is the reference's: ``[num_blocks, block_size,
 num_kv_heads, head_dim]`` (model_runner.py:115).  The product stores pages
-head-major in HBM (see DESIGN.md); the tests convert with
+head-major in HBM; the tests convert with
 ``to_physical`` / ``to_logical`` below, so this file stays a restatement of
 the reference and nothing else.
 

@@ -13,7 +13,7 @@ Follows:
                                   Sampler forbids temperature 0, sampling_params.py:10-11;
                                   greedy == argmax of the logits it would have sampled from)
 
-Two rounding models (SURVEY.md S6):
+Two rounding models:
 * ``rounding="eager"``  every ``.to(bf16)`` in the reference source is a real
   rounding — what the reference modules do on CPU with TORCH_COMPILE_DISABLE=1.
   ``tests/golden/model_*.npz`` (made by running the reference's own modules)
@@ -193,7 +193,7 @@ def alloc_logical_kv(dims: RefDims, num_blocks: int, block_size: int, dtype=torc
 
 
 def model_weight_bytes(dims: RefDims, itemsize: int = 2) -> int:
-    """Bytes of weights one decode step reads (tied head counted once; SURVEY.md section 8d)."""
+    """Bytes of weights one decode step reads (tied head counted once)."""
     d = dims
     per_layer = (d.hidden_size * (d.num_attention_heads + 2 * d.num_key_value_heads) * d.head_dim
                  + d.num_attention_heads * d.head_dim * d.hidden_size

@@ -1,4 +1,4 @@
-"""cuBLAS GEMM latency at the decode shapes of Qwen3-0.6B (library calls on the path; context for DESIGN.md)."""
+"""cuBLAS GEMM latency at the decode shapes of Qwen3-0.6B (library calls on the path)."""
 import json
 import os
 import sys

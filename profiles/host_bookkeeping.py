@@ -3,7 +3,7 @@
     python profiles/host_bookkeeping.py                 # both sides; workloads bench, mixed1024, longctx128 -> one JSON object
     python profiles/host_bookkeeping.py ours|ref NAME   # one side, one workload (what the driver mode runs in subprocesses)
 
-SURVEY.md 8(f) rows 1 and 4: once the GPU step is fast, what the host does per step -- Scheduler.schedule (+ BlockManager),
+Once the GPU step is fast, what the host does per step -- Scheduler.schedule (+ BlockManager),
 the metadata builders (prepare_prefill / prepare_decode / prepare_block_tables), Scheduler.postprocess (+ hash_blocks) --
 bounds tokens/s unless it hides under the GPU step.  This replays a workload with fake tokens (oracle/make_golden.py's driver,
 the one the golden traces were made with, so both sides take identical decisions) and times the three parts per step with

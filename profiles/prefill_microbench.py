@@ -3,7 +3,7 @@
     B200_PREFILL=tc|hmma python profiles/prefill_microbench.py [--paged]
 
 Sequence lengths are those of the benchmark's first prefill step (31 prompts, 15 705 tokens).
-FLOPs = sum_s 4 * Hq * D * (len_q*len_k - len_q^2/2)   (SURVEY.md 8d).
+FLOPs = sum_s 4 * Hq * D * (len_q*len_k - len_q^2/2).
 """
 import argparse
 import json

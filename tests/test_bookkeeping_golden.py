@@ -19,7 +19,7 @@ from nanovllm.sampling_params import SamplingParams
 
 def test_hash_known_answers(golden_dir):
     cases = json.load(open(os.path.join(golden_dir, "hash_kat.json")))
-    assert BlockManager.compute_hash(list(range(256))) == 5218229187174952702
+    assert BlockManager.compute_hash(list(range(256))) == 5218229187174952702      # the reference's own value for this block
     assert BlockManager.compute_hash(list(range(256)), 12345) == 3063373928522455270
     for c in cases:
         assert BlockManager.compute_hash(c["tokens"], c["prefix"]) == c["hash"]
@@ -52,7 +52,7 @@ def test_trace_matches_reference(name, golden_dir):
 
 
 def test_bench_workload_invariants(golden_dir):
-    """The numbers BASELINE.md section 3 quotes for the benchmark request mix."""
+    """The published numbers for the benchmark request mix."""
     gold = json.load(open(os.path.join(golden_dir, "trace_bench.json")))
     w = workloads()["bench"]
     assert sum(len(p) for p in w["prompts"]) == 142827
@@ -63,7 +63,7 @@ def test_bench_workload_invariants(golden_dir):
 
 
 def test_worked_example_block4():
-    """SURVEY.md section 4 worked example (block_size 4): prefix hit, decode slots, chunked prefill."""
+    """Worked example (block_size 4): prefix hit, decode slots, chunked prefill."""
     Sequence.block_size = 4
     Sequence.counter = itertools.count()
     bm = BlockManager(16, 4)

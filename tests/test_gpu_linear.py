@@ -3,7 +3,7 @@ down_proj split-K for batches <= 128 rows; all four in the two-stream decode ste
 
 Reference for every case: torch fp32 matmul of the same bf16 inputs, rounded where the reference rounds
 (F.linear output is bf16, layers/linear.py:51,73,153; SiluAndMul in fp32 on that, layers/activation.py:8-11).
-First run on a B200 in round 2 (all green); part of the default GPU suite since.
+First run on a B200 (all green); part of the default GPU suite since.
 """
 import pytest
 import torch

@@ -224,7 +224,7 @@ def test_decode_bench_shape_vs_oracle_rows():
     from oracle.paged_attention_ref import paged_decode_ref, to_logical
     w = workloads()["bench"]
     lens = [len(p) + 1 for p in w["prompts"]]
-    assert sum(lens) == 143083                           # SURVEY.md 8a: sum of contexts at decode step 0
+    assert sum(lens) == 143083                           # sum of contexts at decode step 0
     hq, hkv, bs = 16, 8, 256
     nblk = sum((c + bs - 1) // bs for c in lens)
     g = torch.Generator(device="cuda").manual_seed(0)
