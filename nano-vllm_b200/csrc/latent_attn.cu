@@ -324,6 +324,24 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         const uint32_t kb = ks_base + (uint32_t)(buf * MMA_BN * DS * 2);
         const __nv_bfloat16* page0 = cache;
         if (one_page) page0 = cache + ((int64_t)bt[j0 / block_size] * block_size + (j0 % block_size)) * D;
+        if (one_page && vec && j0 + MMA_BN <= kmax) {
+            // the usual tile: whole, inside one page, rows of whole 16-byte pieces.  A lane owns the same pieces of every row
+            // of its warp, so a copy costs a pointer step and nothing else.
+            for (int c = lane << 3; c < Dp; c += 256) {
+                const bool col = c < D;                  // pieces past the row's end are zero-filled (nothing is read)
+                const __nv_bfloat16* src = col ? page0 + (int64_t)warp * D + c : cache;
+                const int64_t step = col ? 4 * (int64_t)D : 0;
+                const uint32_t nbytes = col ? 16u : 0u;
+                uint32_t dst = kb + (uint32_t)((warp * DS + c) * 2);
+#pragma unroll
+                for (int r = 0; r < MMA_BN / 4; ++r) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"((const void*)src), "r"(nbytes) : "memory");
+                    src += step;
+                    dst += (uint32_t)(4 * DS * 2);
+                }
+            }
+            return;
+        }
         for (int r = warp; r < MMA_BN; r += 4) {
             const int j = j0 + r;
             const bool in = j < kmax;
