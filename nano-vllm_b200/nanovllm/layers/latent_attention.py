@@ -33,6 +33,8 @@ class LatentAttention:
         rot = m["rot"]
         self.rope_dims = int(rot["dims"])
         assert self.rope_dims <= self.rot_dim and self.rope_dims % 2 == 0
+        if self.kv_rank > 512:
+            raise ValueError(f"kv_rank {self.kv_rank}: the attention kernels hold at most 512 latent columns per query row")
         self.cos_sin = build_interleaved_cos_sin(self.rope_dims, max_position, float(rot["base"]), rot.get("scaling"), device)
         self.rot_key = (self.rope_dims, float(rot["base"]), repr(rot.get("scaling")))
         e = lambda *s: torch.empty(*s, dtype=dtype, device=device)

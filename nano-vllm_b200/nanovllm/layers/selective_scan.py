@@ -22,6 +22,8 @@ class SelectiveScanMixer:
     def __init__(self, width: int, m: dict, dtype, device):
         self.width, self.dtype, self.device = width, dtype, device
         self.inner, self.nstate, self.dt_rank, self.taps = int(m["inner"]), int(m["state"]), int(m["dt_rank"]), int(m["conv"])
+        if self.nstate > 128:
+            raise ValueError(f"state {self.nstate}: the scan kernels hold at most 128 states per channel")
         e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
         C, N, R = self.inner, self.nstate, self.dt_rank
         self.w_in = e(2 * C, width)

@@ -227,7 +227,8 @@ def _scan_layer(m, width, dtype, W, pre, slots):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [dict(inner=48, state=6, dt_rank=5, conv=4), dict(inner=70, state=33, dt_rank=1, conv=1),
-                                   dict(inner=33, state=1, dt_rank=9, conv=6)])
+                                   dict(inner=33, state=1, dt_rank=9, conv=6), dict(inner=136, state=128, dt_rank=4, conv=9),
+                                   dict(inner=300, state=16, dt_rank=12, conv=3), dict(inner=64, state=72, dt_rank=2, conv=2)])
 def test_selective_scan_layer_portions_batches_and_dirty_slots(dtype, shape):
     from types import SimpleNamespace
     cfg = th.config([(th.mamba(**shape), None)])

@@ -56,6 +56,17 @@ def test_rotary_table_matches_plain_implementation(scaling):
         assert abs(table[0, 0].item() - (0.1 * torch.log(torch.tensor(4.0)).item() + 1.0)) < 1e-6
 
 
+def test_shapes_beyond_the_kernels_are_refused_at_construction():
+    from nanovllm.layers.latent_attention import LatentAttention
+    from nanovllm.layers.selective_scan import SelectiveScanMixer
+    with pytest.raises(ValueError, match="kv_rank"):
+        LatentAttention(64, th.latent(kv_rank=520)["mixer"], 1e-5, torch.float32, "cpu", 16)
+    with pytest.raises(ValueError, match="state"):
+        SelectiveScanMixer(64, th.mamba(state=129)["mixer"], torch.float32, "cpu")
+    LatentAttention(64, th.latent(kv_rank=512)["mixer"], 1e-5, torch.float32, "cpu", 16)
+    SelectiveScanMixer(64, th.mamba(state=128)["mixer"], torch.float32, "cpu")
+
+
 def test_state_slots_follow_the_blocks():
     bm = BlockManager(6, 4, num_state_slots=2, prefix_cache=False)
     Sequence.block_size = 4
