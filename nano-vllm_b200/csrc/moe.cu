@@ -10,27 +10,46 @@
 
 namespace {
 
-template <int DUMMY>
-__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top, int32_t* __restrict__ idx,
-                                 float* __restrict__ wgt) {
+// One warp per token: lane l looks at experts l, l + 32, ...; the chosen ones are struck from a per-lane bit mask (so the kernel
+// serves up to 1024 experts), and every round ends in a warp arg-max that prefers the lower index among equal logits.  Lane 0's
+// result is broadcast before it is struck, so exactly the reported expert leaves the candidates whatever the logits hold (a NaN
+// counts as minus infinity): the indices are always valid and distinct.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top,
+                                                        int32_t* __restrict__ idx, float* __restrict__ wgt) {
     B200_PDL_SYNC();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= n) return;
     const float* z = logits + (int64_t)t * ld;
+    constexpr int NONE = 0x7fffffff;
+    uint32_t taken = 0;
     for (int k = 0; k < top; ++k) {
-        int best = -1;
+        int best = NONE;
         float bv = -INFINITY;
-        for (int e = 0; e < E; ++e) {
-            const float v = z[e];
-            bool taken = false;
-            for (int p = 0; p < k; ++p) taken |= (idx[(int64_t)t * top + p] == e);
-            if (!taken && (best < 0 || v > bv)) {
+        for (int i = 0, e = lane; e < E; ++i, e += 32) {
+            float v = z[e];
+            if (!(v == v)) v = -INFINITY;
+            if (!((taken >> i) & 1u) && (best == NONE || v > bv)) {
                 best = e;
                 bv = v;
             }
         }
-        idx[(int64_t)t * top + k] = best;
-        wgt[(int64_t)t * top + k] = sigmoidf_(bv);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int ob = __shfl_xor_sync(0xffffffffu, best, off);
+            if (ob != NONE && (best == NONE || ov > bv || (ov == bv && ob < best))) {
+                bv = ov;
+                best = ob;
+            }
+        }
+        best = __shfl_sync(0xffffffffu, best, 0);
+        bv = __shfl_sync(0xffffffffu, bv, 0);
+        if (best == NONE) best = 0;                       // cannot happen while top <= E; keeps the index in range regardless
+        if ((best & 31) == lane) taken |= 1u << (best >> 5);
+        if (lane == 0) {
+            idx[(int64_t)t * top + k] = best;
+            wgt[(int64_t)t * top + k] = sigmoidf_(bv);
+        }
     }
 }
 
@@ -41,12 +60,14 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
                                                          int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles,
                                                          int32_t* __restrict__ counts) {
     B200_PDL_SYNC();
-    int32_t* cnt = counts;           // [E] pairs per expert
-    int32_t* start = counts + E;     // [E] first sorted row of the expert
+    __shared__ int32_t sh_counts[2048];
+    const bool in_shared = E <= 1024;                            // the usual case: counters in shared memory, `counts` unused
+    int32_t* cnt = in_shared ? sh_counts : counts;               // [E] pairs per expert
+    int32_t* start = in_shared ? sh_counts + 1024 : counts + E;  // [E] first sorted row of the expert
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_rows[i] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[min(max(idx[i], 0), E - 1)], 1);      // an index out of range is counted at the edge, never written through
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -63,7 +84,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     // rows of one expert in ascending pair order would need a stable sort; the order inside an expert changes nothing in
     // the results (rows are independent), so an atomic cursor is enough
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-        const int e = idx[i];
+        const int e = min(max(idx[i], 0), E - 1);
         const int p = start[e] + atomicAdd(&cnt[e], 1);
         sorted_rows[p] = i;
         pos_of[i] = p;
@@ -299,8 +320,9 @@ extern "C" int b200m_moe_tile_rows(void) { return MG_BM; }
 
 extern "C" int b200m_moe_route(const float* logits, int64_t ld, int n, int num_experts, int top, int32_t* idx, float* wgt, void* stream) {
     if (!logits || !idx || !wgt || n < 0 || num_experts <= 0 || top <= 0 || top > num_experts) return B200_EINVAL;
+    if (num_experts > 1024) return B200_EUNSUPPORTED;
     if (n == 0) return B200_OK;
-    B200_LAUNCH((moe_route_kernel<0>), (n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream), logits, ld, n, num_experts, top, idx, wgt);
+    B200_LAUNCH((moe_route_kernel), (n + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream), logits, ld, n, num_experts, top, idx, wgt);
     return b200_launch_status(nullptr);
 }
 

@@ -283,6 +283,30 @@ def test_feed_forward_blocks(dtype, mlp):
     assert rel_err(t if t is not None else f32, want) < (2e-5 if dtype == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("experts,top", [(1, 1), (8, 8), (16, 2), (33, 5), (64, 6), (200, 8)])
+def test_router_picks_the_largest_and_survives_bad_logits(experts, top):
+    """The chosen experts are those of a plain top-k (equal logits: the lower index), with their sigmoid as weight; rows that hold
+    NaN or infinities still get `top` distinct experts in range (such rows occur in warm-up steps over an unwritten cache)."""
+    from nanovllm import mixops
+    g = torch.Generator().manual_seed(experts)
+    z = torch.randn(50, experts + 1, generator=g)                    # one more column than experts: a strided view, as in the layer
+    z[7] = 0.25                                                      # all equal
+    idx, w = mixops.moe_route(z.cuda()[:, :experts], experts, top)
+    want = torch.topk(z[:, :experts], top, dim=1)
+    assert torch.equal(idx.cpu().long()[:7], want.indices[:7]) and torch.equal(idx.cpu().long()[8:], want.indices[8:])
+    assert idx[7].tolist() == list(range(top))
+    assert rel_err(w, torch.sigmoid(want.values)) < 1e-6
+    bad = z.clone()
+    bad[::3] = float("nan")
+    bad[1, ::2] = float("nan")
+    bad[2] = float("inf")
+    bad[4] = -float("inf")
+    idx, _ = mixops.moe_route(bad.cuda()[:, :experts], experts, top)
+    idx = idx.cpu()
+    assert int(idx.min()) >= 0 and int(idx.max()) < experts
+    assert all(len(set(row.tolist())) == top for row in idx)
+
+
 def test_expert_weight_scales_the_input_not_the_output():
     """relu(w x)^2 = w^2 relu(x)^2: with one expert and no shared expert the output is w^2 times the unweighted expert."""
     from nanovllm.layers.moe import RoutedExpertsFF
