@@ -1,8 +1,9 @@
 /*
  * b200_mixers.h -- C ABI of libb200mix.so: sequence mixers and feed-forward pieces of hybrid decoders on B200 (sm_100a):
- * latent attention with a softmax sink over a paged cache of compressed keys, the selective-scan recurrence with
- * per-sequence state slots, routed experts, and the row-wise ops around them (embedding into an fp32 residual stream,
- * residual update + weight-only layer norm, RMS norm, feed-forward activations).
+ * latent attention with a softmax sink over a paged cache of compressed keys, grouped-query attention with a sliding
+ * window and a linear distance bias, the selective-scan recurrence with per-sequence state slots, routed experts, and the
+ * row-wise ops around them (embedding into an fp32 residual stream, residual update + weight-only layer norm, norm on a
+ * sublayer's output, RMS norm, feed-forward activations).
  *
  * Conventions are those of b200_paged_attn.h: 0 or a negative B200_E* code; the caller owns every buffer; nothing
  * synchronises the host and every launch goes to the stream passed in, so a step can be captured in a CUDA graph;
@@ -31,8 +32,18 @@ extern "C" {
 
 int b200m_abi_version(void);
 
-/* out[i, :] = table[ids[i], :] as fp32 (the residual stream). */
-int b200m_embed(const int64_t* ids, const void* table, float* out, int n, int width, int64_t vocab, int is32, void* stream);
+/* out[i, :] = table[ids[i], :] as fp32 (the residual stream); copy (optional) receives the same rows in the table's type. */
+int b200m_embed(const int64_t* ids, const void* table, float* out, void* copy, int n, int width, int64_t vocab, int is32,
+                void* stream);
+
+/* Norm on a sublayer's output, then the residual update: x[r, :] += mult * y / sqrt(mean(y^2) + eps) * (w_offset + w), y =
+ * y[r, :] (activation type) or y32[r, :] (fp32).  copy (optional): the updated rows in the activation type. */
+int b200m_add_normed(float* x, const void* y, const float* y32, const void* w, float mult, float w_offset, void* copy, int rows,
+                     int cols, float eps, int is32, void* stream);
+
+/* out[i, :] = x[r, :] / sqrt(mean(x[r, :]^2) + eps) * (w_offset + w), r = rows_idx[i] (or i when NULL), x the fp32 stream. */
+int b200m_rmsnorm_rows(const float* x, const int32_t* rows_idx, const void* w, float w_offset, void* out, int rows, int cols,
+                       float eps, int is32, void* stream);
 
 /* x[r, :] += a[r, :] + b[r, :] + b32[r, :] (each optional; the terms are summed first), then, unless out is NULL,
  * out[r, :] = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w.  With rows_idx (int32 [rows]) nothing is added and
@@ -68,6 +79,27 @@ int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stri
                            int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
                            int rot_dim, float scale, int is32, int flags, int splits, float* part, void* stream);
 
+/* ---- windowed grouped-query attention ------------------------------------------------------------------------------ */
+
+/* Per token of qkv = [q (q_cols) | k (k_cols) | v (v_cols)] (row stride `stride`): q <- q / rms(q) * q_norm_w over ALL q_cols
+ * at once, in place (skipped when q_norm_w is NULL); cache[slot] = [k / rms(k) * k_norm_w | v] (k copied as is when
+ * k_norm_w is NULL).  k_cols = v_cols = 0: queries only.  slot < 0 skips the store. */
+int b200m_qk_norm_store(void* qkv, int64_t stride, int q_cols, int k_cols, int v_cols, const void* q_norm_w,
+                        const void* k_norm_w, const int32_t* slots, void* cache, int n, float eps, int is32, void* stream);
+
+/* Causal attention of num_heads query heads over num_kv_heads cached key/value heads (head h reads h / (num_heads /
+ * num_kv_heads)): score = q . k * scale - slopes[h] * (i - j) (slopes NULL: no bias), visible keys 0 <= i - j < window
+ * (window <= 0: all j <= i), ordinary softmax.  A cache row is row_elems long: key head g at g * dim, value head g at
+ * v_off + g * vdim.  q [total_q, >= num_heads * dim] with row stride q_stride; out [total_q, num_heads * vdim].
+ * bf16 with dim and vdim in {32, 64, 128} runs on the tensor cores unless flags & 1; everything else on the fp32 FMA pipe.
+ * splits > 1 (bf16 tensor-core decode steps only): the visible keys of every row are shared out over `splits` CTAs whose
+ * partials, fp32 [num_seqs, splits, num_heads, vdim + 2] in `part`, a second launch merges. */
+int b200m_window_attention(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off,
+                           const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
+                           const int32_t* cu_k, const int32_t* ctx_lens, const float* slopes, int window, void* out,
+                           int total_q, int num_seqs, int max_q, int num_heads, int num_kv_heads, int dim, int vdim,
+                           float scale, int is32, int flags, int splits, float* part, void* stream);
+
 /* ---- selective scan ------------------------------------------------------------------------------------------------ */
 
 /* Depthwise causal convolution (w [channels, taps], last tap on the current token) + bias + SiLU; the taps - 1 inputs before
@@ -93,20 +125,31 @@ int b200m_moe_tile_rows(void);
 /* idx / wgt [n, top]: the experts with the largest logits and sigmoid(logit) of each. */
 int b200m_moe_route(const float* logits, int64_t ld, int n, int num_experts, int top, int32_t* idx, float* wgt, void* stream);
 
-/* Groups the n * top (token, choice) pairs by expert, each expert's run padded to a multiple of b200m_moe_tile_rows().
+/* Router with a choice correction, group-limited choice and identity experts.  s = softmax (score_kind 0) or sigmoid (1) of
+ * the num_outputs logits; the choice is made on s + correction (NULL: s) among the experts of the `keep` best of n_groups
+ * equal groups of neighbours (a group's score: its largest choice score; n_groups <= 1: no limit).  wgt = s of the chosen,
+ * divided by their sum + 1e-20 when renorm, times scale.  Outputs e >= num_real are identity experts: idx = -1. */
+int b200m_moe_route_grouped(const float* logits, int64_t ld, int n, int num_outputs, int top, const float* correction,
+                            int n_groups, int keep, int num_real, int score_kind, int renorm, float scale, int32_t* idx,
+                            float* wgt, void* stream);
+
+/* Groups the n * top (token, choice) pairs by expert (pairs with idx < 0 take part in no GEMM: pos_of = -1), each expert's run padded to a multiple of b200m_moe_tile_rows().
  * cap >= round_up(pairs + num_experts * (tile - 1), tile); counts: 2 * num_experts ints of scratch. */
 int b200m_moe_align(const int32_t* idx, int pairs, int num_experts, int32_t* sorted_rows, int cap, int32_t* pos_of,
                     int32_t* tile_expert, int32_t* num_tiles, int32_t* counts, void* stream);
 
 /* C[i, :] = act(A_i . W[expert of i]^T) for every grouped row i.  gather: A_i = A[pair / top] * wgt[pair] (the expert's
- * weighted input); else A_i = A[i].  W [experts, N, K].  act 1 = relu^2.  C is T, or fp32 when out_f32. */
+ * weighted input; wgt NULL: unweighted); else A_i = A[i].  W [experts, N, K].  act 1 = relu^2; act 2 = gated: W holds N/2
+ * gate rows, then N/2 up rows, and C[i, o] = silu(gate_o) * up_o has N/2 columns.  C is T, or fp32 when out_f32. */
 int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* sorted_rows, const float* wgt, int top, int gather,
                    const int32_t* tile_expert, const int32_t* num_tiles, int max_tiles, const void* W, int N, int K, void* C,
                    int out_f32, int act, int is32, void* stream);
 
-/* out[t, :] = sum_k rows[pos_of[t, k], :] + sigmoid(gate_logit[t]) * shared[t, :]  (shared optional; fp32 out). */
+/* out[t, :] = sum_k wgt[t, k] * rows[pos_of[t, k], :] + sigmoid(gate_logit[t]) * shared[t, :]  (fp32 out; wgt NULL: 1; shared
+ * optional; gate_logit NULL: gate 1).  A choice with pos_of < 0 adds wgt[t, k] * ident[t, :] instead (ident NULL: nothing). */
 int b200m_moe_combine(const float* rows, const int32_t* pos_of, int top, const void* shared, const float* gate_logit,
-                      int64_t gate_ld, float* out, int n, int width, int is32, void* stream);
+                      int64_t gate_ld, const float* wgt, const float* ident, float* out, int n, int width, int is32,
+                      void* stream);
 
 #ifdef __cplusplus
 }

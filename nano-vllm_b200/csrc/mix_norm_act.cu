@@ -8,14 +8,58 @@ constexpr int ROW_THREADS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) embed_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table,
-                                                            float* __restrict__ out, int width, int64_t vocab) {
+                                                            float* __restrict__ out, T* __restrict__ copy, int width, int64_t vocab) {
     B200_PDL_SYNC();
     const int row = blockIdx.x;
     int64_t id = ids[row];
     if (id < 0 || id >= vocab) id = 0;
     const T* src = table + id * width;
     float* dst = out + (int64_t)row * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = ldf(src + c);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const T v = src[c];
+        dst[c] = ldf(&v);
+        if (copy) copy[(int64_t)row * width + c] = v;
+    }
+}
+
+// Norm on a sublayer's OUTPUT, then the residual update:  x[row] += mult * y[row] / sqrt(mean(y^2) + eps) * (w_offset + w).
+// y is the branch output in the activation type, or (y32) in fp32.  `copy`, when given, receives the updated row in the
+// activation type: the operand of the next sublayer's projections, which read the stream itself.
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS) add_normed_kernel(float* __restrict__ x, const T* __restrict__ y,
+                                                                 const float* __restrict__ y32, const T* __restrict__ w, float mult,
+                                                                 float w_offset, T* __restrict__ copy, int cols, float eps) {
+    B200_PDL_SYNC();
+    __shared__ float red[ROW_THREADS / 32];
+    const int64_t base = (int64_t)blockIdx.x * cols;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = y32 ? y32[base + c] : ldf(y + base + c);
+        q = fmaf(v, v, q);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)cols + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = y32 ? y32[base + c] : ldf(y + base + c);
+        const float r = fmaf(mult, v * rstd * (w_offset + ldf(w + c)), x[base + c]);
+        x[base + c] = r;
+        if (copy) stf(copy + base + c, r);
+    }
+}
+
+// out[i] = x[row] / sqrt(mean(x[row]^2) + eps) * (w_offset + w) for row = rows_idx[i] (or i) of an fp32 stream.
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS) rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows_idx,
+                                                                   const T* __restrict__ w, float w_offset, T* __restrict__ out,
+                                                                   int cols, float eps) {
+    B200_PDL_SYNC();
+    __shared__ float red[ROW_THREADS / 32];
+    const int64_t row = rows_idx ? rows_idx[blockIdx.x] : blockIdx.x;
+    const float* xr = x + row * cols;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) q = fmaf(xr[c], xr[c], q);
+    const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)cols + eps);
+    T* o = out + (int64_t)blockIdx.x * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) stf(o + c, xr[c] * rstd * (w_offset + ldf(w + c)));
 }
 
 // x[row] += (a[row] + b[row] + b32[row])  (each term optional), then out[i] = LN(x[row]) * w, where the statistics are the
@@ -121,13 +165,33 @@ __global__ void __launch_bounds__(256) ff_act_vec_kernel(const __nv_bfloat16* __
 
 }  // namespace
 
-extern "C" int b200m_abi_version(void) { return 1; }
+extern "C" int b200m_abi_version(void) { return 2; }
 
-extern "C" int b200m_embed(const int64_t* ids, const void* table, float* out, int n, int width, int64_t vocab, int is32, void* stream) {
+extern "C" int b200m_embed(const int64_t* ids, const void* table, float* out, void* copy, int n, int width, int64_t vocab, int is32,
+                           void* stream) {
     if (!ids || !table || !out || n < 0 || width <= 0 || vocab <= 0) return B200_EINVAL;
     if (n == 0) return B200_OK;
     B200M_DISPATCH(is32, B200_LAUNCH((embed_kernel<T>), n, ROW_THREADS, 0, static_cast<cudaStream_t>(stream), ids,
-                                     static_cast<const T*>(table), out, width, vocab));
+                                     static_cast<const T*>(table), out, static_cast<T*>(copy), width, vocab));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_add_normed(float* x, const void* y, const float* y32, const void* w, float mult, float w_offset, void* copy,
+                                int rows, int cols, float eps, int is32, void* stream) {
+    if (!x || (!y && !y32) || !w || rows < 0 || cols <= 0) return B200_EINVAL;
+    if (rows == 0) return B200_OK;
+    B200M_DISPATCH(is32, B200_LAUNCH((add_normed_kernel<T>), rows, ROW_THREADS, 0, static_cast<cudaStream_t>(stream), x,
+                                     static_cast<const T*>(y), y32, static_cast<const T*>(w), mult, w_offset,
+                                     static_cast<T*>(copy), cols, eps));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_rmsnorm_rows(const float* x, const int32_t* rows_idx, const void* w, float w_offset, void* out, int rows,
+                                  int cols, float eps, int is32, void* stream) {
+    if (!x || !w || !out || rows < 0 || cols <= 0) return B200_EINVAL;
+    if (rows == 0) return B200_OK;
+    B200M_DISPATCH(is32, B200_LAUNCH((rmsnorm_rows_kernel<T>), rows, ROW_THREADS, 0, static_cast<cudaStream_t>(stream), x, rows_idx,
+                                     static_cast<const T*>(w), w_offset, static_cast<T*>(out), cols, eps));
     return b200_launch_status(nullptr);
 }
 

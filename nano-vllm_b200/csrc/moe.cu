@@ -2,6 +2,9 @@
 // step stays graph-capturable), grouped expert GEMMs over the grouped rows, and the weighted combine.
 //
 //   moe_route_kernel  : scores = sigmoid(logits) in fp32; the `top` largest per token with their scores as weights
+//   moe_route_grouped_kernel: scores = softmax(logits) (or sigmoid); the choice is made on score + correction, among the experts of
+//                       the best groups only; weights are the plain scores of the chosen, renormalised and scaled; experts past
+//                       `num_real` are identity experts (no tensors: index -1, handled by the combine)
 //   moe_align_kernel  : counting sort of the (token, choice) pairs by expert; every expert's run is padded to a multiple of
 //                       the GEMM's row tile so one tile never spans two experts
 //   moe_gemm_kernel   : C[i, :] = act(A[src(i), :] * scale(i)) . W[e(i)]^T, one expert per row tile
@@ -53,6 +56,124 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     }
 }
 
+constexpr int RG_MAX = 1024;       // experts (identity ones included) the grouped router serves
+constexpr int RG_WARPS = 4;
+
+// One warp per token.  s = softmax(z) over all `E` router outputs (score_kind 0) or sigmoid(z) (1); choice score c = s +
+// correction.  The E outputs form `n_groups` equal groups of neighbours; a group's score is its largest c, and only experts of
+// the `keep` best groups can be chosen (with n_groups <= 1 or keep >= n_groups: all).  The `top` largest c among those win;
+// their weights are s (without the correction), divided by their sum + 1e-20 when `renorm`, times `scale`.  Equal scores go
+// to the lower index; a NaN counts as minus infinity.  idx is the expert, or -1 for the identity experts e >= num_real.
+__global__ void __launch_bounds__(RG_WARPS * 32) moe_route_grouped_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top,
+                                                                          const float* __restrict__ correction, int n_groups, int keep,
+                                                                          int num_real, int score_kind, int renorm, float scale,
+                                                                          int32_t* __restrict__ idx, float* __restrict__ wgt) {
+    B200_PDL_SYNC();
+    __shared__ float sh_s[RG_WARPS][RG_MAX];          // plain scores
+    __shared__ float sh_g[RG_WARPS][RG_MAX];          // group scores; after the group choice: 1 = open, 0 = closed
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RG_WARPS + warp;
+    if (t >= n) return;
+    const float* z = logits + (int64_t)t * ld;
+    float* sc = sh_s[warp];
+    float* gs = sh_g[warp];
+    constexpr int NONE = 0x7fffffff;
+    if (score_kind == 0) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(z[e] - mx);
+            sc[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) sc[e] *= inv;
+    } else {
+        for (int e = lane; e < E; e += 32) sc[e] = sigmoidf_(z[e]);
+    }
+    __syncwarp();
+    const bool grouped = n_groups > 1 && keep < n_groups;
+    const int gsize = grouped ? E / n_groups : E;
+    if (grouped) {
+        for (int gi = lane; gi < n_groups; gi += 32) {
+            float best = -INFINITY;
+            for (int e = gi * gsize; e < (gi + 1) * gsize; ++e) {
+                float c = sc[e] + (correction ? correction[e] : 0.f);
+                if (!(c == c)) c = -INFINITY;
+                best = fmaxf(best, c);
+            }
+            gs[gi] = best;
+        }
+        __syncwarp();
+        uint32_t open = 0;                            // bit i: group lane + 32 i is kept
+        for (int k = 0; k < keep; ++k) {
+            int best = NONE;
+            float bv = -INFINITY;
+            for (int i = 0, gi = lane; gi < n_groups; ++i, gi += 32) {
+                const float v = gs[gi];
+                if (!((open >> i) & 1u) && (best == NONE || v > bv)) {
+                    best = gi;
+                    bv = v;
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                const int ob = __shfl_xor_sync(0xffffffffu, best, off);
+                if (ob != NONE && (best == NONE || ov > bv || (ov == bv && ob < best))) {
+                    bv = ov;
+                    best = ob;
+                }
+            }
+            best = __shfl_sync(0xffffffffu, best, 0);
+            if (best != NONE && (best & 31) == lane) open |= 1u << (best >> 5);
+        }
+        __syncwarp();
+        for (int i = 0, gi = lane; gi < n_groups; ++i, gi += 32) gs[gi] = ((open >> i) & 1u) ? 1.f : 0.f;
+        __syncwarp();
+    }
+    uint32_t taken = 0;
+    float wsum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = NONE;
+        float bv = -INFINITY;
+        for (int i = 0, e = lane; e < E; ++i, e += 32) {
+            if ((taken >> i) & 1u) continue;
+            if (grouped && gs[e / gsize] == 0.f) continue;
+            float c = sc[e] + (correction ? correction[e] : 0.f);
+            if (!(c == c)) c = -INFINITY;
+            if (best == NONE || c > bv) {
+                best = e;
+                bv = c;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int ob = __shfl_xor_sync(0xffffffffu, best, off);
+            if (ob != NONE && (best == NONE || ov > bv || (ov == bv && ob < best))) {
+                bv = ov;
+                best = ob;
+            }
+        }
+        best = __shfl_sync(0xffffffffu, best, 0);
+        if (best == NONE) best = 0;                   // only if fewer than `top` experts are open; keeps the index in range
+        if ((best & 31) == lane) taken |= 1u << (best >> 5);
+        const float w = sc[best];
+        wsum += w;
+        if (lane == 0) {
+            idx[(int64_t)t * top + k] = best < num_real ? best : -1;
+            wgt[(int64_t)t * top + k] = w;
+        }
+    }
+    __syncwarp();
+    const float f = (renorm ? 1.0f / (wsum + 1e-20f) : 1.0f) * scale;
+    for (int k = lane; k < top; k += 32) wgt[(int64_t)t * top + k] *= f;
+}
+
 // One CTA.  pairs = n * top entries of idx.  Outputs: sorted_rows[cap] (pair index, or -1 for padding), pos_of[pairs]
 // (where each pair went), tile_expert[max_tiles], num_tiles[0].  counts: scratch of 2 * E ints.
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restrict__ idx, int pairs, int E, int bm,
@@ -67,7 +188,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_rows[i] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[min(max(idx[i], 0), E - 1)], 1);      // an index out of range is counted at the edge, never written through
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+        if (idx[i] >= 0) atomicAdd(&cnt[min(idx[i], E - 1)], 1);      // a negative index is a pair without an expert GEMM; one too large is counted at the edge, never written through
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -84,7 +206,11 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     // rows of one expert in ascending pair order would need a stable sort; the order inside an expert changes nothing in
     // the results (rows are independent), so an atomic cursor is enough
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-        const int e = min(max(idx[i], 0), E - 1);
+        if (idx[i] < 0) {
+            pos_of[i] = -1;
+            continue;
+        }
+        const int e = min(idx[i], E - 1);
         const int p = start[e] + atomicAdd(&cnt[e], 1);
         sorted_rows[p] = i;
         pos_of[i] = p;
@@ -95,7 +221,9 @@ constexpr int MG_BM = 64, MG_BN = 64, MG_BK = 32;
 constexpr int MG_TM = MG_BM / 16;          // rows per thread of the FMA kernel (16 x 16 threads)
 
 // A rows: src_rows == nullptr -> row i of A itself (the grouped intermediate); else pair = sorted_rows[i], token = pair / top,
-// A row = tokens[token] * wgt[pair] (rounded to T: it is the expert's input tensor).  act: 0 none, 1 relu^2.
+// A row = tokens[token] * wgt[pair] (rounded to T: it is the expert's input tensor; wgt == nullptr: the token's row as is).
+// act: 0 none, 1 relu^2, 2 gated: W = [gate rows (N/2) ; up rows (N/2)] and C[i, o] = silu(gate_o) * up_o has N/2 columns; a CTA
+// then stages the gate rows and the up rows of its N/2-column slice side by side.
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, int64_t a_stride, const int32_t* __restrict__ sorted_rows,
                                                        const float* __restrict__ wgt, int top, bool gather,
@@ -110,11 +238,13 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
     __shared__ float sc[MG_BM];
     const int e = tile_expert[tile];
     const T* We = W + (int64_t)e * N * K;
-    const int row0 = tile * MG_BM, col0 = blockIdx.x * MG_BN;
+    const bool gated = act == 2;
+    const int half = N >> 1;
+    const int row0 = tile * MG_BM, col0 = blockIdx.x * (gated ? MG_BN / 2 : MG_BN);
     if (threadIdx.x < MG_BM) {
         const int p = sorted_rows[row0 + threadIdx.x];
         src[threadIdx.x] = p < 0 ? -1 : (gather ? p / top : row0 + (int)threadIdx.x);
-        sc[threadIdx.x] = (p >= 0 && gather) ? wgt[p] : 1.0f;
+        sc[threadIdx.x] = (p >= 0 && gather && wgt) ? wgt[p] : 1.0f;
     }
     __syncthreads();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, MG_TM rows x 4 columns each
@@ -125,13 +255,18 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
             float v = 0.f;
             if (src[r] >= 0 && k0 + k < K) {
                 v = ldf(A + (int64_t)src[r] * a_stride + k0 + k);
-                if (gather) v = rnd<T>(v * sc[r]);
+                if (gather && wgt) v = rnd<T>(v * sc[r]);
             }
             As[r][k] = v;
         }
         for (int i = threadIdx.x; i < MG_BN * MG_BK; i += 256) {
             const int c = i / MG_BK, k = i % MG_BK;
-            Ws[c][k] = (col0 + c < N && k0 + k < K) ? ldf(We + (int64_t)(col0 + c) * K + k0 + k) : 0.f;
+            int wr = col0 + c, lim = N;
+            if (gated) {
+                wr = c < MG_BN / 2 ? col0 + c : half + col0 + c - MG_BN / 2;
+                lim = c < MG_BN / 2 ? half : N;
+            }
+            Ws[c][k] = (wr < lim && k0 + k < K) ? ldf(We + (int64_t)wr * K + k0 + k) : 0.f;
         }
         __syncthreads();
 #pragma unroll 8
@@ -152,6 +287,14 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
     for (int r = 0; r < MG_TM; ++r) {
         const int row = ty * MG_TM + r;
         if (src[row] < 0) continue;
+        if (gated) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int col = col0 + tx + 16 * j;
+                if (col < half) stf(C + (int64_t)(row0 + row) * half + col, siluf_(acc[r][j]) * acc[r][j + 2]);
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int col = col0 + tx + 16 * j;
@@ -206,27 +349,35 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
     __shared__ float sc[MG_BM];
     const int e = tile_expert[tile];
     const __nv_bfloat16* We = W + (int64_t)e * N * K;
-    const int row0 = tile * MG_BM, col0 = blockIdx.x * MM_BN;
+    const bool gated = act == 2;                       // tile row 2 o' = gate row, 2 o' + 1 = up row of output column col0 + o'
+    const int half = N >> 1;
+    const int row0 = tile * MG_BM, col0 = blockIdx.x * (gated ? MM_BN / 2 : MM_BN);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wr = warp >> 2, wc = warp & 3;                            // this warp's 32 rows and 32 columns of the tile
     if (tid < MG_BM) {
         const int p = sorted_rows[row0 + tid];
         src[tid] = p < 0 ? -1 : (gather ? p / top : row0 + tid);
-        sc[tid] = (p >= 0 && gather) ? wgt[p] : 1.0f;
+        sc[tid] = (p >= 0 && gather && wgt) ? wgt[p] : 1.0f;
     }
     __syncthreads();
     auto load_stage = [&](int st, int k0) {
         for (int i = tid; i < MM_BN * (MM_BK / 8); i += 256) {          // weights: 128 rows x 8 chunks of 16 bytes
             const int r = i >> 3, c = (i & 7) << 3;
-            const bool ok = col0 + r < N && k0 + c < K;
-            cp_async16(smem_u32(&Bs[st][r][c]), ok ? (const void*)(We + (int64_t)(col0 + r) * K + k0 + c) : (const void*)We, ok ? 16 : 0);
+            int wr = col0 + r;
+            bool ok = wr < N && k0 + c < K;
+            if (gated) {
+                wr = col0 + (r >> 1);
+                ok = wr < half && k0 + c < K;
+                wr += (r & 1) ? half : 0;
+            }
+            cp_async16(smem_u32(&Bs[st][r][c]), ok ? (const void*)(We + (int64_t)wr * K + k0 + c) : (const void*)We, ok ? 16 : 0);
         }
         for (int i = tid; i < MG_BM * (MM_BK / 8); i += 256) {          // input rows: gathered, weighted, rounded
             const int r = i >> 3, c = (i & 7) << 3;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (src[r] >= 0 && k0 + c < K) {
                 v = *reinterpret_cast<const uint4*>(A + (int64_t)src[r] * a_stride + k0 + c);
-                if (gather) {
+                if (gather && wgt) {
                     float f[8];
                     unpack8(v, f);
 #pragma unroll
@@ -281,6 +432,14 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
         for (int hh = 0; hh < 2; ++hh) {
             const int row = wr * 32 + mt * 16 + g + 8 * hh;
             if (src[row] < 0) continue;
+            if (gated) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int col = col0 + wc * 16 + nt * 4 + t4;
+                    if (col < half) stf(C + (int64_t)(row0 + row) * half + col, siluf_(acc[mt][nt][2 * hh]) * acc[mt][nt][2 * hh + 1]);
+                }
+                continue;
+            }
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -297,18 +456,27 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
         }
 }
 
-// out[t, :] = sum_k rows[pos_of[t * top + k], :] + sigmoid(gate_logit[t]) * shared[t, :]
+// out[t, :] = sum_k w[t, k] * rows[pos_of[t * top + k], :] + sigmoid(gate_logit[t]) * shared[t, :]   (w = 1 without wgt; gate = 1
+// without gate_logit).  A choice without a grouped row (pos_of < 0: an identity expert) contributes w[t, k] * ident[t, :].
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ pos_of, int top,
                                    const T* __restrict__ shared, const float* __restrict__ gate_logit, int64_t gate_ld,
-                                   float* __restrict__ out, int n, int width) {
+                                   const float* __restrict__ wgt, const float* __restrict__ ident, float* __restrict__ out, int n,
+                                   int width) {
     B200_PDL_SYNC();
     const int t = blockIdx.x;
     float g = 0.f;
     if (shared) g = gate_logit ? sigmoidf_(gate_logit[(int64_t)t * gate_ld]) : 1.0f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float a = 0.f;
-        for (int k = 0; k < top; ++k) a += rows[(int64_t)pos_of[(int64_t)t * top + k] * width + c];
+        for (int k = 0; k < top; ++k) {
+            const int p = pos_of[(int64_t)t * top + k];
+            const float w = wgt ? wgt[(int64_t)t * top + k] : 1.0f;
+            if (p >= 0)
+                a = fmaf(w, rows[(int64_t)p * width + c], a);
+            else if (ident)
+                a = fmaf(w, ident[(int64_t)t * width + c], a);
+        }
         if (shared) a = fmaf(g, ldf(shared + (int64_t)t * width + c), a);
         out[(int64_t)t * width + c] = a;
     }
@@ -326,6 +494,21 @@ extern "C" int b200m_moe_route(const float* logits, int64_t ld, int n, int num_e
     return b200_launch_status(nullptr);
 }
 
+extern "C" int b200m_moe_route_grouped(const float* logits, int64_t ld, int n, int num_outputs, int top, const float* correction,
+                                       int n_groups, int keep, int num_real, int score_kind, int renorm, float scale, int32_t* idx,
+                                       float* wgt, void* stream) {
+    if (!logits || !idx || !wgt || n < 0 || num_outputs <= 0 || top <= 0 || top > num_outputs || num_real < 0 || num_real > num_outputs)
+        return B200_EINVAL;
+    if (n_groups > 1 && (num_outputs % n_groups || keep <= 0)) return B200_EINVAL;
+    if (n_groups > 1 && keep < n_groups && top > keep * (num_outputs / n_groups)) return B200_EINVAL;
+    if (score_kind < 0 || score_kind > 1) return B200_EINVAL;
+    if (num_outputs > RG_MAX) return B200_EUNSUPPORTED;
+    if (n == 0) return B200_OK;
+    B200_LAUNCH((moe_route_grouped_kernel), (n + RG_WARPS - 1) / RG_WARPS, RG_WARPS * 32, 0, static_cast<cudaStream_t>(stream), logits, ld,
+                n, num_outputs, top, correction, n_groups, keep, num_real, score_kind, renorm, scale, idx, wgt);
+    return b200_launch_status(nullptr);
+}
+
 extern "C" int b200m_moe_align(const int32_t* idx, int pairs, int num_experts, int32_t* sorted_rows, int cap, int32_t* pos_of,
                                int32_t* tile_expert, int32_t* num_tiles, int32_t* counts, void* stream) {
     if (!idx || !sorted_rows || !pos_of || !tile_expert || !num_tiles || !counts || pairs < 0 || num_experts <= 0) return B200_EINVAL;
@@ -339,12 +522,14 @@ extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* so
                               const int32_t* tile_expert, const int32_t* num_tiles, int max_tiles, const void* W, int N, int K,
                               void* C, int out_f32, int act, int is32, void* stream) {
     if (!A || !sorted_rows || !tile_expert || !num_tiles || !W || !C || N <= 0 || K <= 0 || max_tiles < 0) return B200_EINVAL;
-    if (gather && (!wgt || top <= 0)) return B200_EINVAL;
+    if (gather && top <= 0) return B200_EINVAL;
+    if (act < 0 || act > 2 || (act == 2 && (N & 1))) return B200_EINVAL;
     if (max_tiles == 0) return B200_OK;
+    const int n_out = act == 2 ? N / 2 : N;                // output columns
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool tc = !is32 && (K % 8 == 0) && (a_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) % 16 == 0);
     if (tc) {
-        dim3 g2((N + MM_BN - 1) / MM_BN, max_tiles);
+        dim3 g2(act == 2 ? (n_out + MM_BN / 2 - 1) / (MM_BN / 2) : (N + MM_BN - 1) / MM_BN, max_tiles);
         using bf = __nv_bfloat16;
         const size_t smem = 2 * (size_t)(MG_BM + MM_BN) * MM_LD * sizeof(bf);
         cudaError_t ce = out_f32 ? cudaFuncSetAttribute(moe_gemm_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -361,7 +546,7 @@ extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* so
                         tile_expert, num_tiles, static_cast<const bf*>(W), N, K, static_cast<bf*>(C), act);
         return b200_launch_status(nullptr);
     }
-    dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+    dim3 grid(act == 2 ? (n_out + MG_BN / 2 - 1) / (MG_BN / 2) : (N + MG_BN - 1) / MG_BN, max_tiles);
     if (out_f32) {
         B200M_DISPATCH(is32, B200_LAUNCH((moe_gemm_kernel<T, float>), grid, 256, 0, st, static_cast<const T*>(A), a_stride, sorted_rows,
                                          wgt, top, gather != 0, tile_expert, num_tiles, static_cast<const T*>(W), N, K,
@@ -375,10 +560,11 @@ extern "C" int b200m_moe_gemm(const void* A, int64_t a_stride, const int32_t* so
 }
 
 extern "C" int b200m_moe_combine(const float* rows, const int32_t* pos_of, int top, const void* shared, const float* gate_logit,
-                                 int64_t gate_ld, float* out, int n, int width, int is32, void* stream) {
+                                 int64_t gate_ld, const float* wgt, const float* ident, float* out, int n, int width, int is32,
+                                 void* stream) {
     if (!rows || !pos_of || !out || n < 0 || width <= 0 || top <= 0) return B200_EINVAL;
     if (n == 0) return B200_OK;
     B200M_DISPATCH(is32, B200_LAUNCH((moe_combine_kernel<T>), n, 256, 0, static_cast<cudaStream_t>(stream), rows, pos_of, top,
-                                     static_cast<const T*>(shared), gate_logit, gate_ld, out, n, width));
+                                     static_cast<const T*>(shared), gate_logit, gate_ld, wgt, ident, out, n, width));
     return b200_launch_status(nullptr);
 }

@@ -49,7 +49,13 @@ SIGNATURES = {
 _f32p = _vp
 MIX_SIGNATURES = {
     "b200m_abi_version": (_i, []),
-    "b200m_embed": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
+    "b200m_embed": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
+    "b200m_add_normed": (_i, [_vp, _vp, _vp, _vp, _f, _f, _vp, _i, _i, _f, _i, _vp]),
+    "b200m_rmsnorm_rows": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _f, _i, _vp]),
+    "b200m_qk_norm_store": (_i, [_vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _i, _vp]),
+    "b200m_window_attention": (_i, [_vp, _i64, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i,
+                                    _f, _i, _i, _i, _vp, _vp]),
+    "b200m_moe_route_grouped": (_i, [_vp, _i64, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "b200m_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200m_rmsnorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _f, _i, _vp]),
     "b200m_ff_act": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp]),
@@ -63,7 +69,7 @@ MIX_SIGNATURES = {
     "b200m_moe_route": (_i, [_vp, _i64, _i, _i, _i, _vp, _vp, _vp]),
     "b200m_moe_align": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "b200m_moe_gemm": (_i, [_vp, _i64, _vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _i, _i, _i, _vp]),
-    "b200m_moe_combine": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
+    "b200m_moe_combine": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }
 
 _lib = None

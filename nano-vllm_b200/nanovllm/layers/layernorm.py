@@ -35,3 +35,17 @@ class ResidualLayerNorm:
     def __call__(self, x, a=None, b=None, b32=None, rows_idx=None):
         from .. import mixops
         return mixops.add_layernorm(x, self.weight, self.eps, a=a, b=b, b32=b32, rows_idx=rows_idx)
+
+
+class SublayerOutputNorm:
+    """RMS norm on a sublayer's OUTPUT with a weight stored around zero, fused with the scaled residual update of an fp32
+    stream: ``x += mult * y / sqrt(mean(y^2) + eps) * (1 + w)``.  ``copy`` receives the updated rows in the activation type
+    (the next sublayer's GEMM operand; the sublayers read the stream itself, not a normed copy)."""
+
+    def __init__(self, width: int, eps: float, dtype, device):
+        self.eps = eps
+        self.weight = torch.zeros(width, dtype=dtype, device=device)
+
+    def __call__(self, x, y, mult: float, copy=None) -> None:
+        from .. import mixops
+        mixops.add_normed(x, y, self.weight, mult, self.eps, w_offset=1.0, copy=copy)

@@ -5,6 +5,13 @@ Routed:  z = W_router h (fp32), s = sigmoid(z); the `top` experts with the large
          the weight scales the expert's INPUT:  out = sum_e expert_e(s_e h),  expert(x) = W_down relu(W_up x)^2;
          an optional shared expert of the same form runs for every token, scaled by sigmoid(W_sg h).
 
+Group-routed (``GroupRoutedExpertsFF``):
+         z = W_router h (fp32), s = softmax(z) over all router outputs; the choice is made on s + correction, only among the
+         experts of the `keep` best of `count` equal groups of neighbours (a group's score: its largest s + correction); the
+         weights are the chosen experts' s, divided by their sum + 1e-20, times a constant, and scale the expert's OUTPUT:
+         out = sum_e w_e expert_e(h),  expert(x) = W_down (silu(W_gate x) * (W_up x));  the last `identity` router outputs are
+         identity experts without tensors (expert(x) = x); an optional ungated shared expert of the same form is added.
+
 The routed path groups (token, choice) pairs by expert on the device and runs two grouped GEMMs over the grouped rows; the
 router (and the shared gate, one more row of the same fp32 GEMM) never leave fp32.
 """
@@ -86,3 +93,74 @@ class RoutedExpertsFF:
             shared = F.linear(mixops.ff_act(F.linear(h, self.sh_up), mixops.FF_RELU2), self.sh_down)
             gate = logits[:, self.experts]
         return None, mixops.moe_combine(rows, pos_of, self.top, n, shared, gate)
+
+
+class GroupRoutedExpertsFF:
+    def __init__(self, width: int, mlp: dict, dtype, device):
+        r = mlp["router"]
+        self.identity = int(r.get("identity") or 0)
+        self.experts, self.top = int(r["experts"]), int(r["top"])          # experts with tensors; identity ones come after them
+        self.outputs = self.experts + self.identity
+        g = r.get("groups") or {}
+        self.groups, self.keep = int(g.get("count") or 1), int(g.get("keep") or 1)
+        self.route_scale = float(r.get("scale", 1.0))
+        if self.outputs % self.groups or not 0 < self.keep <= self.groups or self.top > self.keep * (self.outputs // self.groups):
+            raise ValueError("router groups must divide the router outputs and leave at least `top` experts open")
+        self.ff = int(mlp["expert"]["ff"])
+        shared = mlp.get("shared")
+        self.shared_ff = int(shared["ff"]) if shared else 0
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.w_gate_up = e(max(self.experts, 1), 2 * self.ff, width)        # per expert: gate rows, then up rows
+        self.w_down = e(max(self.experts, 1), width, self.ff)
+        self.w_router = torch.zeros(self.outputs, width, dtype=torch.float32, device=device)
+        self.correction = torch.zeros(self.outputs, dtype=torch.float32, device=device)
+        if shared:
+            self.sh_gate_up, self.sh_down = e(2 * self.shared_ff, width), e(width, self.shared_ff)
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        parts = leaf.split(".")
+        if parts[0].startswith("e") and parts[0][1:].isdigit() and len(parts) == 2 and int(parts[0][1:]) < self.experts:
+            k = int(parts[0][1:])
+            if parts[1] == "gate":
+                self.w_gate_up[k, :self.ff].copy_(w)
+            elif parts[1] == "up":
+                self.w_gate_up[k, self.ff:].copy_(w)
+            elif parts[1] == "down":
+                self.w_down[k].copy_(w)
+            else:
+                return False
+        elif leaf == "router":
+            self.w_router.copy_(w.float())
+        elif leaf == "correction":
+            self.correction.copy_(w.float().view(-1))
+        elif leaf == "shared.gate" and self.shared_ff:
+            self.sh_gate_up[:self.shared_ff].copy_(w)
+        elif leaf == "shared.up" and self.shared_ff:
+            self.sh_gate_up[self.shared_ff:].copy_(w)
+        elif leaf == "shared.down" and self.shared_ff:
+            self.sh_down.copy_(w)
+        else:
+            return False
+        return True
+
+    def weight_shapes(self, width: int) -> dict:
+        out = {"router": (self.outputs, width), "correction": (self.outputs,)}
+        for k in range(self.experts):
+            out.update({f"e{k}.gate": (self.ff, width), f"e{k}.up": (self.ff, width), f"e{k}.down": (width, self.ff)})
+        if self.shared_ff:
+            out.update({"shared.gate": (self.shared_ff, width), "shared.up": (self.shared_ff, width), "shared.down": (width, self.shared_ff)})
+        return out
+
+    def forward(self, h: torch.Tensor, x32: torch.Tensor) -> torch.Tensor:
+        """h: the block's input in the activation type, x32: the same rows in fp32 (router input, identity experts) -> fp32."""
+        n = h.shape[0]
+        logits = F.linear(x32, self.w_router)
+        idx, wgt = mixops.moe_route_grouped(logits, self.outputs, self.top, self.correction, self.groups, self.keep, self.experts,
+                                            scale=self.route_scale)
+        sorted_rows, pos_of, tile_expert, num_tiles = mixops.moe_align(idx, max(self.experts, 1))
+        inter = mixops.moe_gemm(h, sorted_rows, tile_expert, num_tiles, self.w_gate_up, top=self.top, act=2, gather=True)
+        rows = mixops.moe_gemm(inter, sorted_rows, tile_expert, num_tiles, self.w_down, out_f32=True)
+        shared = None
+        if self.shared_ff:
+            shared = F.linear(mixops.ff_act(F.linear(h, self.sh_gate_up), mixops.FF_SILU_MUL), self.sh_down)
+        return mixops.moe_combine(rows, pos_of, self.top, n, shared, None, wgt=wgt, ident=x32 if self.identity else None)

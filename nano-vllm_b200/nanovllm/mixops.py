@@ -66,13 +66,39 @@ def _call(name, *args):
     nat.check_mix(getattr(nat.load_mix(), name)(*args))
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """ids int64 [n] -> fp32 [n, width]."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None, copy: torch.Tensor | None = None) -> torch.Tensor:
+    """ids int64 [n] -> fp32 [n, width]; ``copy`` (table's dtype, [n, width]) receives the same rows unconverted."""
     assert ids.dtype == torch.int64 and ids.is_contiguous() and table.is_contiguous()
     n, width = ids.numel(), table.shape[1]
     if out is None:
         out = torch.empty(n, width, dtype=torch.float32, device=table.device)
-    _call("b200m_embed", ids.data_ptr(), table.data_ptr(), out.data_ptr(), n, width, table.shape[0], _is32(table), _stream())
+    assert copy is None or (copy.dtype == table.dtype and copy.is_contiguous() and copy.shape == out.shape)
+    _call("b200m_embed", ids.data_ptr(), table.data_ptr(), out.data_ptr(), _p(copy), n, width, table.shape[0], _is32(table), _stream())
+    return out
+
+
+def add_normed(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, mult: float, eps: float, w_offset: float = 0.0,
+               copy: torch.Tensor | None = None) -> None:
+    """x (fp32 [rows, cols], in place) += mult * rms_norm(y) * (w_offset + weight): the norm sits on the sublayer's output.
+    y: the activation type of ``weight``, or fp32.  ``copy`` ([rows, cols], weight's dtype): the updated rows, rounded."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2 and y.is_contiguous() and y.shape == x.shape
+    is32 = _is32(weight)
+    y32 = y.dtype == torch.float32 and not is32
+    if not y32:
+        _same(is32, y)
+    assert copy is None or (copy.dtype == weight.dtype and copy.is_contiguous() and copy.shape == x.shape)
+    _call("b200m_add_normed", x.data_ptr(), None if y32 else y.data_ptr(), y.data_ptr() if y32 else None, weight.data_ptr(),
+          mult, w_offset, _p(copy), x.shape[0], x.shape[1], eps, is32, _stream())
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, w_offset: float = 0.0, rows_idx: torch.Tensor | None = None):
+    """RMS norm of rows of the fp32 stream (all, or those named by int32 ``rows_idx``) -> weight's dtype."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    assert rows_idx is None or rows_idx.dtype == torch.int32
+    n = x.shape[0] if rows_idx is None else rows_idx.numel()
+    out = torch.empty(n, x.shape[1], dtype=weight.dtype, device=x.device)
+    _call("b200m_rmsnorm_rows", x.data_ptr(), _p(rows_idx), weight.data_ptr(), w_offset, out.data_ptr(), n, x.shape[1], eps,
+          _is32(weight), _stream())
     return out
 
 
@@ -166,6 +192,54 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, c
     return out
 
 
+# ---- windowed grouped-query attention --------------------------------------------------------------------------------------
+def qk_norm_store(qkv: torch.Tensor, q_cols: int, k_cols: int, v_cols: int, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None,
+                  slots: torch.Tensor | None, cache: torch.Tensor | None, eps: float) -> None:
+    """qkv [n, q_cols + k_cols + v_cols]: whole-projection RMS norm of q in place; [norm(k) | v] -> cache rows at ``slots``."""
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= q_cols + k_cols + v_cols
+    is32 = _is32(qkv)
+    _same(is32, q_norm, k_norm, cache)
+    if k_cols + v_cols:
+        assert slots.dtype == torch.int32 and slots.numel() == qkv.shape[0] and cache.is_contiguous() and cache.shape[-1] == k_cols + v_cols
+    _call("b200m_qk_norm_store", qkv.data_ptr(), qkv.stride(0), q_cols, k_cols, v_cols, _p(q_norm), _p(k_norm), _p(slots), _p(cache),
+          qkv.shape[0], eps, is32, _stream())
+
+
+def window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, block_size: int, spans: StepSpans,
+                     heads: int, kv_heads: int, dim: int, vdim: int, scale: float, slopes: torch.Tensor | None = None,
+                     window: int = 0, fma: bool = False, splits: int | None = None) -> torch.Tensor:
+    """q [n, >= heads * dim] (row-strided view), cache [slots, kv_heads * (dim + vdim)] -> [n, heads * vdim]."""
+    n = q.shape[0]
+    assert q.dim() == 2 and q.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == kv_heads * (dim + vdim)
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == heads)
+    is32 = _is32(q)
+    _same(is32, cache)
+    out = torch.empty(n, heads * vdim, dtype=q.dtype, device=q.device)
+    part, nsplit = None, 1
+    if splits is None:
+        splits = window_attention_splits(spans, block_tables.shape[1] * block_size, window, kv_heads) if (not is32 and not fma) else 1
+    if splits > 1 and spans.cu_q is None and not is32 and not fma:
+        nsplit = splits
+        part = torch.empty(spans.num_seqs * nsplit * heads * (vdim + 2), dtype=torch.float32, device=q.device)
+        ops.LAUNCHES[0] += 1
+    _call("b200m_window_attention", q.data_ptr(), q.stride(0), cache.data_ptr(), cache.shape[-1], kv_heads * dim,
+          block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
+          _p(slopes), int(window), out.data_ptr(), n, spans.num_seqs, spans.max_q, heads, kv_heads, dim, vdim, scale, is32,
+          int(fma), nsplit, _p(part), _stream())
+    return out
+
+
+def window_attention_splits(spans: StepSpans, max_keys: int, window: int, kv_heads: int) -> int:
+    """How many CTAs share the visible keys of one decode row: enough for about two CTAs per SM, at least two 64-key tiles each.
+    Static per (batch rows, table width), so the choice also holds inside a captured graph."""
+    if spans.cu_q is not None:
+        return 1
+    keys = min(max_keys, window) if window > 0 else max_keys
+    tiles = -(-keys // 64)
+    return max(1, min(tiles // 2, 32, (2 * _sm_count()) // max(spans.num_seqs * kv_heads, 1)))
+
+
 # ---- selective scan ------------------------------------------------------------------------------------------------------
 SCAN_CHUNK = 64          # tokens per chunk of the chunk-parallel form
 
@@ -232,6 +306,21 @@ def moe_route(logits: torch.Tensor, num_experts: int, top: int):
     return idx, wgt
 
 
+def moe_route_grouped(logits: torch.Tensor, num_outputs: int, top: int, correction: torch.Tensor | None = None, groups: int = 1,
+                      keep: int = 1, num_real: int | None = None, sigmoid: bool = False, renorm: bool = True, scale: float = 1.0):
+    """logits fp32 [n, >= num_outputs] -> (idx int32 [n, top], weights fp32 [n, top]).  Softmax (or sigmoid) scores; the choice
+    is made on score + correction within the `keep` best of `groups` equal groups; weights are the plain scores of the chosen,
+    renormalised and scaled.  Router outputs from ``num_real`` on are identity experts: idx -1."""
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == num_outputs)
+    n = logits.shape[0]
+    idx = torch.empty(n, top, dtype=torch.int32, device=logits.device)
+    wgt = torch.empty(n, top, dtype=torch.float32, device=logits.device)
+    _call("b200m_moe_route_grouped", logits.data_ptr(), logits.stride(0), n, num_outputs, top, _p(correction), groups, keep,
+          num_outputs if num_real is None else num_real, int(sigmoid), int(renorm), scale, idx.data_ptr(), wgt.data_ptr(), _stream())
+    return idx, wgt
+
+
 def moe_align(idx: torch.Tensor, num_experts: int):
     """-> (sorted_rows [cap], pos_of [pairs], tile_expert [cap / tile], num_tiles [1]) int32, all on the device."""
     pairs = idx.numel()
@@ -248,28 +337,32 @@ def moe_align(idx: torch.Tensor, num_experts: int):
 
 
 def moe_gemm(A: torch.Tensor, sorted_rows, tile_expert, num_tiles, W: torch.Tensor, wgt: torch.Tensor | None = None, top: int = 1,
-             act: int = 0, out_f32: bool = False) -> torch.Tensor:
-    """W [experts, N, K].  With ``wgt``: row i is token (pair // top) of A times the pair's weight; else row i of A."""
+             act: int = 0, out_f32: bool = False, gather: bool = False) -> torch.Tensor:
+    """W [experts, N, K].  With ``wgt`` or ``gather``: row i is token (pair // top) of A (times the pair's weight); else row i
+    of A.  act 1: relu^2; act 2: W = [gate rows ; up rows], the result silu(gate) * up has N / 2 columns."""
     assert A.dim() == 2 and A.stride(1) == 1 and W.dim() == 3 and W.is_contiguous() and A.shape[1] == W.shape[2]
     is32 = _is32(A)
     _same(is32, W)
     cap = sorted_rows.numel()
-    out = torch.empty(cap, W.shape[1], dtype=torch.float32 if out_f32 else A.dtype, device=A.device)
-    _call("b200m_moe_gemm", A.data_ptr(), A.stride(0), sorted_rows.data_ptr(), _p(wgt), top, int(wgt is not None),
+    out = torch.empty(cap, W.shape[1] // 2 if act == 2 else W.shape[1], dtype=torch.float32 if out_f32 else A.dtype, device=A.device)
+    _call("b200m_moe_gemm", A.data_ptr(), A.stride(0), sorted_rows.data_ptr(), _p(wgt), top, int(wgt is not None or gather),
           tile_expert.data_ptr(), num_tiles.data_ptr(), tile_expert.numel(), W.data_ptr(), W.shape[1], W.shape[2], out.data_ptr(),
           int(out_f32), act, is32, _stream())
     return out
 
 
 def moe_combine(rows: torch.Tensor, pos_of: torch.Tensor, top: int, n: int, shared: torch.Tensor | None = None,
-                gate_logit: torch.Tensor | None = None) -> torch.Tensor:
-    """rows fp32 [cap, width] -> fp32 [n, width]; gate_logit: fp32 column view [n] (any stride)."""
+                gate_logit: torch.Tensor | None = None, wgt: torch.Tensor | None = None, ident: torch.Tensor | None = None) -> torch.Tensor:
+    """rows fp32 [cap, width] -> fp32 [n, width]; gate_logit: fp32 column view [n] (any stride); wgt fp32 [n, top] weights the
+    choices' rows; ident fp32 [n, width] stands in for the row of a choice without an expert (pos_of < 0)."""
     assert rows.dtype == torch.float32 and rows.is_contiguous()
     width = rows.shape[1]
     out = torch.empty(n, width, dtype=torch.float32, device=rows.device)
     is32 = _is32(shared) if shared is not None else 1
     gld = gate_logit.stride(0) if gate_logit is not None else 0
     assert gate_logit is None or gate_logit.dtype == torch.float32
-    _call("b200m_moe_combine", rows.data_ptr(), pos_of.data_ptr(), top, _p(shared), _p(gate_logit), gld, out.data_ptr(), n, width,
-          is32, _stream())
+    assert wgt is None or (wgt.dtype == torch.float32 and wgt.is_contiguous() and wgt.numel() == n * top)
+    assert ident is None or (ident.dtype == torch.float32 and ident.is_contiguous() and ident.shape == out.shape)
+    _call("b200m_moe_combine", rows.data_ptr(), pos_of.data_ptr(), top, _p(shared), _p(gate_logit), gld, _p(wgt), _p(ident),
+          out.data_ptr(), n, width, is32, _stream())
     return out

@@ -23,8 +23,18 @@ def _tafopel_config(raw: dict):
     return TafopelConfig(raw)
 
 
-MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel}
-CONFIG_READERS = {"Tafopel": _tafopel_config}
+def _tipetar():
+    from .tipetar import TipetarForCausalLM
+    return TipetarForCausalLM
+
+
+def _tipetar_config(raw: dict):
+    from .tipetar import TipetarConfig
+    return TipetarConfig(raw)
+
+
+MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel, "Tipetar": _tipetar}
+CONFIG_READERS = {"Tafopel": _tafopel_config, "Tipetar": _tipetar_config}
 
 
 def architecture_of(hf_config) -> str:

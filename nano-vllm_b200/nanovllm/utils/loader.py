@@ -78,7 +78,8 @@ def _random_fill_named(model, seed: int) -> int:
             dt = torch.exp(torch.rand(shape, generator=gen, device=dev) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
             w = dt + torch.log(-torch.expm1(-dt))
         elif len(shape) == 1:
-            w = torch.randn(shape, generator=gen, device=dev) * 0.1 + (0.0 if leaf in ("b", "sink") else 1.0)
+            centre = 0.0 if leaf in ("b", "sink") or name.endswith(tuple(getattr(model, "zero_centred", ()))) else 1.0
+            w = torch.randn(shape, generator=gen, device=dev) * 0.1 + centre
         elif name == "embed":
             w = torch.randn(shape, generator=gen, device=dev)
         else:
