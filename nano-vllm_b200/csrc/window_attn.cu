@@ -178,6 +178,287 @@ int launch_window_fma(const void* q, int64_t q_stride, const void* cache, int ro
     return b200_launch_status(nullptr);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form (bf16).  The 64 rows of a CTA are (token, head-in-group) pairs of one sequence and one key/value head, 16 per
+// warp; key tiles of 64 cache rows (keys DK wide, values DV wide) arrive by 16-byte asynchronous copies into a two-deep ring, the
+// next tile in flight while the current one is multiplied.  S = Q K^T and O += P V are mma.sync m16n8k16 with fp32 accumulators
+// in registers; scale, distance bias, window and causal mask are applied to the S fragments; the softmax runs in base 2.
+// Tiles start at multiples of 64 keys; rows past the last visible key are zero-filled (never read: their page may be absent).
+// splits > 1 (single-token steps): blockIdx.z also names a share of the key tiles and the CTA leaves unnormalised partials.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int WM_BM = 64, WM_BN = 64;
+constexpr float WM_LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void wm_cp16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void wm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void wm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void wm_ldsm(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void wm_ldsm_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void wm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t wm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache, int row_elems, int v_off,
+    const int32_t* __restrict__ block_tables, int bt_stride, int block_size, const int32_t* __restrict__ cu_q,
+    const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, const float* __restrict__ slopes, int window,
+    __nv_bfloat16* __restrict__ out, int H, int G, float scale, int splits, float* __restrict__ part) {
+    B200_PDL_SYNC();
+    constexpr int KS = DK + 8, VS = DV + 8;               // row strides: 16-byte multiples, odd in 16-byte units (conflict-free ldmatrix)
+    extern __shared__ __align__(16) unsigned char wm_smem[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);       // [64][KS]
+    __nv_bfloat16* Ks = Qs + WM_BM * KS;                                 // [2][64][KS]
+    __nv_bfloat16* Vs = Ks + 2 * WM_BN * KS;                             // [2][64][VS]
+    const int s = blockIdx.y, rep = H / G;
+    const int g = blockIdx.z / splits, split = blockIdx.z - g * splits;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    const int nrows = sp.qlen * rep;
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * WM_BM;               // the last rows of a portion see the most keys: launched first
+    if (row0 >= nrows) return;
+    const int first = sp.klen - sp.qlen;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t4 = lane & 3;
+    const int i_lo = row0 / rep, i_hi = min(sp.qlen - 1, (row0 + WM_BM - 1) / rep);
+    const int kmax = first + i_hi + 1;
+    const int kmin = window > 0 ? max(0, first + i_lo - window + 1) : 0;
+    int t_lo = kmin / WM_BN, t_hi = (kmax + WM_BN - 1) / WM_BN;          // key tiles [t_lo, t_hi)
+    if (splits > 1) {
+        const int nt = t_hi - t_lo;
+        const int a = t_lo + (int)(((int64_t)nt * split) / splits), b = t_lo + (int)(((int64_t)nt * (split + 1)) / splits);
+        t_lo = a;
+        t_hi = b;
+    }
+    const int32_t* bt = block_tables + (int64_t)s * bt_stride;
+
+    auto load_tile = [&](int buf, int t) {
+        const int j0 = t * WM_BN;
+        __nv_bfloat16* kd = Ks + buf * WM_BN * KS;
+        __nv_bfloat16* vd = Vs + buf * WM_BN * VS;
+        constexpr int KC = DK / 8, VC = DV / 8;
+        for (int e = tid; e < WM_BN * (KC + VC); e += 128) {
+            const int r = e / (KC + VC), c = e - r * (KC + VC);
+            const int j = j0 + r;
+            const bool ok = j < kmax;
+            const __nv_bfloat16* src = cache;
+            if (ok) {
+                const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
+                src = cache + slot * row_elems + (c < KC ? g * DK + c * 8 : v_off + g * DV + (c - KC) * 8);
+            }
+            const uint32_t dst = c < KC ? smem_u32(kd + r * KS + c * 8) : smem_u32(vd + r * VS + (c - KC) * 8);
+            wm_cp16(dst, src, ok ? 16 : 0);
+        }
+        wm_commit();
+    };
+    if (t_lo < t_hi) load_tile(0, t_lo);
+
+    // queries of this CTA's rows (plain loads; visible after the loop's first barrier)
+    for (int e = tid; e < WM_BM * (DK / 8); e += 128) {
+        const int r = e / (DK / 8), c = e - r * (DK / 8);
+        const int rr = row0 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (rr < nrows) {
+            const int i = rr / rep, h = g * rep + (rr - i * rep);
+            v = *reinterpret_cast<const uint4*>(q + (int64_t)(sp.q0 + i) * q_stride + (int64_t)h * DK + c * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + r * KS + c * 8) = v;
+    }
+
+    // this thread's two rows: warp * 16 + gq and + 8
+    int pos_r[2];
+    float slope2[2];
+    bool live[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int rr = row0 + warp * 16 + gq + 8 * hh;
+        live[hh] = rr < nrows;
+        const int i = live[hh] ? rr / rep : 0;
+        pos_r[hh] = first + i;
+        slope2[hh] = (live[hh] && slopes) ? slopes[g * rep + (rr - i * rep)] * WM_LOG2E : 0.f;
+    }
+    // keys any row of this warp sees: [w_lo, w_hi]
+    const int wr0 = row0 + warp * 16, wr1 = min(nrows - 1, wr0 + 15);
+    const int w_hi = wr0 < nrows ? first + wr1 / rep : -1;
+    const int w_lo = window > 0 ? max(0, first + wr0 / rep - window + 1) : 0;
+    const float scale2 = scale * WM_LOG2E;
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) {
+            load_tile(buf ^ 1, t + 1);
+            wm_wait<1>();
+        } else {
+            wm_wait<0>();
+        }
+        __syncthreads();
+        const int j0 = t * WM_BN;
+        if (w_hi >= j0 && w_lo < j0 + WM_BN) {                           // warp-uniform: some row of this warp sees some key of the tile
+            const __nv_bfloat16* kt = Ks + buf * WM_BN * KS;
+            const __nv_bfloat16* vt = Vs + buf * WM_BN * VS;
+            float sc[WM_BN / 8][4];
+#pragma unroll
+            for (int n = 0; n < WM_BN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+            const uint32_t a_base = smem_u32(Qs + (warp * 16 + (lane & 15)) * KS + ((lane >> 4) << 3));
+            const uint32_t b_base = smem_u32(kt + ((lane & 7) + ((lane >> 4) << 3)) * KS + (((lane >> 3) & 1) << 3));
+#pragma unroll
+            for (int kk = 0; kk < DK; kk += 16) {
+                uint32_t a0, a1, a2, a3;
+                wm_ldsm(a_base + kk * 2, a0, a1, a2, a3);
+#pragma unroll
+                for (int np = 0; np < WM_BN / 16; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    wm_ldsm(b_base + (np * 16 * KS + kk) * 2, b0, b1, b2, b3);
+                    wm_mma(sc[2 * np], a0, a1, a2, a3, b0, b1);
+                    wm_mma(sc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+            // scale, bias, mask; running maximum
+            float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+            for (int n = 0; n < WM_BN / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int hh = e >> 1;
+                    const int j = j0 + n * 8 + 2 * t4 + (e & 1);
+                    const int dist = pos_r[hh] - j;
+                    const bool ok = live[hh] && dist >= 0 && (window <= 0 || dist < window);
+                    const float v = ok ? fmaf(sc[n][e], scale2, -slope2[hh] * (float)dist) : -INFINITY;
+                    sc[n][e] = v;
+                    m_new[hh] = fmaxf(m_new[hh], v);
+                }
+            float alpha[2], m_use[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                m_new[hh] = fmaxf(m_new[hh], __shfl_xor_sync(0xffffffffu, m_new[hh], 1));
+                m_new[hh] = fmaxf(m_new[hh], __shfl_xor_sync(0xffffffffu, m_new[hh], 2));
+                m_use[hh] = m_new[hh] == -INFINITY ? 0.f : m_new[hh];    // a row that has seen nothing yet
+                alpha[hh] = exp2f(m_run[hh] - m_use[hh]);
+                m_run[hh] = m_new[hh];
+                l_run[hh] *= alpha[hh];
+            }
+#pragma unroll
+            for (int n = 0; n < WM_BN / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(sc[n][e] - m_use[e >> 1]);
+                    sc[n][e] = p;
+                    l_run[e >> 1] += p;
+                }
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) {
+                o[n][0] *= alpha[0];
+                o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1];
+                o[n][3] *= alpha[1];
+            }
+            // O += P V: P from the S fragments, V through transposing loads
+            const uint32_t v_base = smem_u32(vt + ((lane & 7) + (((lane >> 3) & 1) << 3)) * VS + ((lane >> 4) << 3));
+#pragma unroll
+            for (int kk = 0; kk < WM_BN / 16; ++kk) {
+                const uint32_t a0 = wm_pack(sc[2 * kk][0], sc[2 * kk][1]), a1 = wm_pack(sc[2 * kk][2], sc[2 * kk][3]);
+                const uint32_t a2 = wm_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), a3 = wm_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+                for (int np = 0; np < DV / 16; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    wm_ldsm_t(v_base + (kk * 16 * VS + np * 16) * 2, b0, b1, b2, b3);
+                    wm_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
+                    wm_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();                                                 // the tile is consumed: its buffer may be refilled
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int rr = row0 + warp * 16 + gq + 8 * hh;
+        if (rr >= nrows) continue;
+        const int i = rr / rep, h = g * rep + (rr - i * rep);
+        if (splits > 1) {                                                // decode rows only (one token per sequence): i == 0
+            float* pp = part + (((int64_t)s * splits + split) * H + h) * (DV + 2);
+            if (t4 == 0) {
+                pp[0] = m_run[hh];
+                pp[1] = l_run[hh];
+            }
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) {
+                pp[2 + n * 8 + 2 * t4] = o[n][2 * hh];
+                pp[2 + n * 8 + 2 * t4 + 1] = o[n][2 * hh + 1];
+            }
+        } else {
+            const float inv = 1.0f / l_run[hh];
+            __nv_bfloat16* op = out + ((int64_t)(sp.q0 + i) * H + h) * DV;
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n)
+                *reinterpret_cast<uint32_t*>(op + n * 8 + 2 * t4) = wm_pack(o[n][2 * hh] * inv, o[n][2 * hh + 1] * inv);
+        }
+    }
+}
+
+// out[s, h, :] = sum_k acc_k 2^(m_k - M) / sum_k l_k 2^(m_k - M) over the `splits` partials of a decode row
+__global__ void window_merge_kernel(const float* __restrict__ part, const int32_t* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out,
+                                    int H, int vdim, int splits) {
+    B200_PDL_SYNC();
+    const int s = blockIdx.x, h = blockIdx.y;
+    if (ctx_lens[s] <= 0) return;
+    const float* base = part + ((int64_t)s * splits * H + h) * (vdim + 2);
+    const int64_t step = (int64_t)H * (vdim + 2);
+    float M = -INFINITY;
+    for (int k = 0; k < splits; ++k) M = fmaxf(M, base[k * step]);
+    float L = 0.f;
+    for (int k = 0; k < splits; ++k) L += base[k * step + 1] * exp2f(base[k * step] - M);
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+        float a = 0.f;
+        for (int k = 0; k < splits; ++k) {
+            const float mk = base[k * step];
+            if (mk != -INFINITY) a = fmaf(base[k * step + 2 + c], exp2f(mk - M), a);
+        }
+        out[((int64_t)s * H + h) * vdim + c] = __float2bfloat16_rn(a * inv);
+    }
+}
+
+template <int DK, int DV>
+int launch_window_mma(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
+                      int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
+                      const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
+                      float* part, cudaStream_t stream) {
+    using bf = __nv_bfloat16;
+    const size_t smem = sizeof(bf) * ((size_t)WM_BM * (DK + 8) + 2 * (size_t)WM_BN * (DK + 8) + 2 * (size_t)WM_BN * (DV + 8));
+    int rc = wa_ensure_smem(window_attn_mma_kernel<DK, DV>, smem);
+    if (rc != B200_OK) return rc;
+    dim3 grid((max_q * (H / G) + WM_BM - 1) / WM_BM, num_seqs, G * splits);
+    B200_LAUNCH((window_attn_mma_kernel<DK, DV>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
+                static_cast<const bf*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens, slopes,
+                window, static_cast<bf*>(out), H, G, scale, splits, part);
+    rc = b200_launch_status(nullptr);
+    if (rc != B200_OK || splits <= 1) return rc;
+    B200_LAUNCH((window_merge_kernel), dim3(num_seqs, H), DV < 64 ? 32 : 64, 0, stream, part, ctx_lens, static_cast<bf*>(out), H, DV, splits);
+    return b200_launch_status(nullptr);
+}
+
 }  // namespace
 
 extern "C" int b200m_qk_norm_store(void* qkv, int64_t stride, int q_cols, int k_cols, int v_cols, const void* q_norm_w,
@@ -204,9 +485,27 @@ extern "C" int b200m_window_attention(const void* q, int64_t q_stride, const voi
     if (total_q == 0 || num_seqs == 0 || max_q <= 0) return B200_OK;
     if (vdim > 512) return B200_EUNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    (void)flags;
-    (void)splits;
-    (void)part;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) % 16 == 0) && q_stride % 8 == 0 &&
+                         row_elems % 8 == 0 && v_off % 8 == 0;
+    if (!is32 && !(flags & 1) && aligned && (dim == 32 || dim == 64 || dim == 128) && (vdim == 32 || vdim == 64 || vdim == 128)) {
+        if (cu_q != nullptr || splits < 1) splits = 1;                  // keys are split for single-token steps only
+        if (splits > 1 && !part) return B200_EINVAL;
+#define WA_MMA(DK, DV)                                                                                                           \
+    if (dim == DK && vdim == DV)                                                                                                 \
+        return launch_window_mma<DK, DV>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,  \
+                                         ctx_lens, slopes, window, out, num_seqs, max_q, num_heads, num_kv_heads, scale, splits, \
+                                         part, st)
+        WA_MMA(32, 32);
+        WA_MMA(32, 64);
+        WA_MMA(32, 128);
+        WA_MMA(64, 32);
+        WA_MMA(64, 64);
+        WA_MMA(64, 128);
+        WA_MMA(128, 32);
+        WA_MMA(128, 64);
+        WA_MMA(128, 128);
+#undef WA_MMA
+    }
 #define WA_FMA(OACC)                                                                                                             \
     B200M_DISPATCH(is32, return (launch_window_fma<T, OACC>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride,       \
                                                             block_size, cu_q, cu_k, ctx_lens, slopes, window, out, num_seqs,     \

@@ -1,0 +1,461 @@
+"""Tipetar on the GPU against the plain implementation (oracle/tipetar_ref.py, float64, whole sequences, no cache):
+every mechanism alone, then whole models through the engine's runner, scheduler bookkeeping and cache manager --
+prompts, token-by-token decoding, portions, mixed batches, reused pages -- and greedy generation through LLM."""
+import math
+
+import pytest
+import torch
+
+import tipetar_helpers as th
+from oracle import tipetar_ref as ref
+from test_gpu_tafopel import Replay, rel_err, spans_varlen
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 3e-4, "bfloat16": 6e-2}
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+# mechanisms alone
+# ---------------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cols", [44, 200, 1000])
+def test_norm_on_the_branch_output_and_scaled_residual(dtype, cols):
+    from nanovllm import mixops
+    g = torch.Generator().manual_seed(cols)
+    x = torch.randn(7, cols, generator=g) * 3 + 1.5
+    w = (0.3 * torch.randn(cols, generator=g)).to(DT[dtype])
+    for y in (torch.randn(7, cols, generator=g).to(DT[dtype]) * 5, torch.randn(7, cols, generator=g) * 0.01):       # branch in the activation type / in fp32
+        xd = x.cuda()
+        copy = torch.empty(7, cols, dtype=DT[dtype], device="cuda")
+        mixops.add_normed(xd, y.cuda(), w.cuda(), 0.37, 1e-5, w_offset=1.0, copy=copy)
+        want = x.double() + 0.37 * ref.out_norm(y.double(), w.double(), 1e-5)
+        assert rel_err(xd, want) < 2e-6                                     # the stream itself stays fp32 in both formats
+        assert torch.equal(copy, xd.to(DT[dtype]))
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device="cuda")
+    sel = mixops.rmsnorm_rows(xd, w.cuda(), 1e-5, w_offset=1.0, rows_idx=rows)
+    assert rel_err(sel, ref.out_norm(xd.double().cpu()[[5, 0, 5]], w.double(), 1e-5)) < (2e-6 if dtype == "float32" else 4e-3)
+    assert torch.equal(mixops.rmsnorm_rows(xd, w.cuda(), 1e-5, w_offset=1.0)[[5, 0, 5]], sel)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_projection_norms_and_cache_rows(dtype):
+    """The query norm takes one statistic over all heads of a token (not one per head); keys likewise; values are stored as they are;
+    a token with slot -1 stores nothing."""
+    from nanovllm import mixops
+    g = torch.Generator().manual_seed(3)
+    H, G, d, vd, n = 3, 2, 12, 20, 9
+    qc, kc, vc = H * d, G * d, G * vd
+    qkv = (torch.randn(n, qc + kc + vc, generator=g) * torch.linspace(0.2, 4.0, qc + kc + vc)).to(DT[dtype])     # heads of very different size
+    wq, wk = (1 + 0.3 * torch.randn(qc, generator=g)).to(DT[dtype]), (1 + 0.3 * torch.randn(kc, generator=g)).to(DT[dtype])
+    slots = torch.tensor([4, 0, 17, -1, 3, 9, 8, 30, 1], dtype=torch.int32)
+    cache = torch.full((32, kc + vc), 7.0, dtype=DT[dtype], device="cuda")
+    dev = qkv.cuda().clone()
+    mixops.qk_norm_store(dev, qc, kc, vc, wq.cuda(), wk.cuda(), slots.cuda(), cache, 1e-5)
+    x = qkv.double()
+    tol = 2e-6 if dtype == "float32" else 4e-3
+    assert rel_err(dev[:, :qc], ref.unit_rms(x[:, :qc], 1e-5) * wq.double()) < tol
+    wantk = ref.unit_rms(x[:, qc:qc + kc], 1e-5) * wk.double()
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0:
+            assert rel_err(cache[s, :kc], wantk[t]) < tol and torch.equal(cache[s, kc:].cpu(), qkv[t, qc + kc:])
+    untouched = [s for s in range(32) if s not in slots.tolist()]
+    assert bool((cache[untouched] == 7.0).all())
+    # queries only (a layer that reads another layer's keys)
+    dev2 = qkv[:, :qc].contiguous().cuda()
+    mixops.qk_norm_store(dev2, qc, 0, 0, wq.cuda(), None, None, None, 1e-5)
+    assert torch.equal(dev2, dev[:, :qc])
+
+
+def paged(rows, pages, bs, dtype, total_pages, stale=None):
+    """rows [L, D] -> cache [total_pages * bs, D] with token j at pages[j // bs] * bs + j % bs; the rest holds `stale`."""
+    cache = torch.zeros(total_pages * bs, rows.shape[1], dtype=DT[dtype]) if stale is None else stale.to(DT[dtype]).repeat(total_pages * bs, 1)
+    for j in range(rows.shape[0]):
+        cache[int(pages[j // bs]) * bs + j % bs] = rows[j].to(DT[dtype])
+    return cache
+
+
+def run_attention(mixops, q_rows, first, kv, pages, bs, dtype, H, G, d, vd, scale, window, decode, **kw):
+    """q_rows [n, H * d] are the queries of positions first .. first + n - 1 of one sequence whose cache rows are `kv`."""
+    n = q_rows.shape[0]
+    bt = pages[None, :].to(torch.int32).cuda().contiguous()
+    if decode:
+        assert n == 1
+        sp = mixops.StepSpans(1, 1, None, None, torch.tensor([first + 1], dtype=torch.int32, device="cuda"))
+    else:
+        sp = spans_varlen([n], [first + n])
+    sl = ref.slopes(H).float().cuda()
+    return mixops.window_attention(q_rows.to(DT[dtype]).cuda(), kv.cuda(), bt, bs, sp, H, G, d, vd, scale, sl, window, **kw)
+
+
+PATHS = [dict(fma=True), dict(), dict(splits=3)]          # fp32-pipe kernel, tensor-core kernel, tensor-core kernel with the keys split
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("bs,window", [(16, 50), (64, 64), (64, 200), (16, 1000)])
+def test_attention_sees_exactly_the_window(dtype, bs, window):
+    """One key is made to dominate head 1 (a large multiple of its query): the head's output must be that key's value while the key
+    is inside the window and must not feel it one position later.  The key sits at page borders, at position 0 and far back; the
+    query is the last row of a portion or a single decoded token; pages are scrambled and hold a stale dominating row beyond
+    the sequence's end and in unused pages."""
+    from nanovllm import mixops
+    H, G, d, vd, L = 4, 2, 32, 32, 330
+    g = torch.Generator().manual_seed(bs + window)
+    npages = (L + bs - 1) // bs + 1
+    pages = torch.randperm(40, generator=g)[:npages]
+    for star in (0, bs - 1, bs, 3 * bs - 1, 129, L - 2):
+        q = torch.randn(L, H * d, generator=g)
+        k = torch.randn(L, G * d, generator=g) * 0.3
+        v = torch.randn(L, G * vd, generator=g)
+        for pos in sorted({star, star + 1, star + window - 1, star + window, L - 1} & set(range(star, L))):
+            qq = q.clone()
+            kk = k.clone()
+            u = qq[pos, d:2 * d] / qq[pos, d:2 * d].norm()
+            kk[star, :d] = 40.0 * u                           # head 1 (key/value head 0) of position `pos` looks straight at it
+            qq[pos, d:2 * d] = 8.0 * u
+            stale = torch.cat([60.0 * u.repeat(G), torch.full((G * vd,), 1e3)])
+            cache = paged(torch.cat([kk, v], 1), pages, bs, dtype, 40, stale=stale)
+            kv_t = torch.stack([cache[int(pages[j // bs]) * bs + j % bs] for j in range(L)]).double()
+            qd = qq.to(DT[dtype]).double()
+            want = ref.windowed_attention(qd[:pos + 1], kv_t[:pos + 1, :G * d], kv_t[:pos + 1, G * d:], H, G, 0.25, window)
+            inside = pos - star < window
+            if inside:                                        # the planted key takes (nearly) all of head 1's weight
+                assert rel_err(want[pos, vd:2 * vd], kv_t[star, G * d:G * d + vd]) < 0.02
+            tol = 1e-5 if dtype == "float32" else 1.5e-2
+            for kw in PATHS if dtype == "bfloat16" else PATHS[:1]:
+                got = run_attention(mixops, qq[pos:pos + 1], pos, cache, pages, bs, dtype, H, G, d, vd, 0.25, window, True, **kw)
+                assert rel_err(got[0], want[pos]) < tol, (star, pos, "decode", kw)
+                n = min(5, pos + 1)
+                got = run_attention(mixops, qq[pos - n + 1:pos + 1], pos - n + 1, cache, pages, bs, dtype, H, G, d, vd, 0.25, window, False, **kw)
+                assert rel_err(got, want[pos - n + 1:pos + 1]) < tol, (star, pos, "portion", kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_distance_bias_and_head_groups(dtype):
+    """With equal keys everywhere the weights follow the bias alone: head h prefers recent tokens with slope 2^(-8 (h + 1) / H), so the
+    output is a known average of the values; and each query head reads the values of its own key/value head."""
+    from nanovllm import mixops
+    H, G, d, vd, L, bs, window = 6, 3, 16, 16, 90, 16, 70
+    pages = torch.arange(8)
+    k = torch.ones(L, G * d)
+    v = torch.arange(L, dtype=torch.float32)[:, None].repeat(1, G * vd) + torch.arange(G).repeat_interleave(vd)[None, :] * 100.0
+    cache = paged(torch.cat([k, v], 1), pages, bs, dtype, 8)
+    q = torch.zeros(1, H * d)
+    pos = L - 1
+    stored = v.to(DT[dtype]).double()
+    for kw in (PATHS if dtype == "bfloat16" else PATHS[:1]):
+        got = run_attention(mixops, q, pos, cache, pages, bs, dtype, H, G, d, vd, 0.5, window, True, **kw).double().cpu().view(H, vd)
+        for h in range(H):
+            j = torch.arange(pos - window + 1, pos + 1)
+            p = torch.softmax(-(2.0 ** (-8.0 * (h + 1) / H)) * (pos - j).double(), 0)
+            want = (p * stored[j, (h // (H // G)) * vd]).sum()
+            assert abs(got[h, 0].item() - want.item()) < (1e-3 if dtype == "float32" else 1.5), (h, kw)
+
+
+@pytest.mark.parametrize("bs", [16, 64])
+@pytest.mark.parametrize("shape", [(8, 2, 64, 64, 70), (4, 4, 32, 32, 33), (16, 2, 128, 128, 500), (6, 2, 64, 32, 64), (3, 1, 12, 20, 9),
+                                   (5, 5, 8, 4, 0), (2, 1, 128, 64, 1), (12, 4, 32, 128, 129)])
+def test_attention_shapes_and_batches(shape, bs):
+    """Head counts, head sizes and windows on every kernel path, three unequal sequences in one step (a long portion, a short one that
+    starts mid-page, a single token), compared with each sequence alone in float64."""
+    from nanovllm import mixops
+    H, G, d, vd, window = shape
+    g = torch.Generator().manual_seed(H * 100 + d)
+    lens, news = [300, 75, 140], [167, 11, 1]
+    tables = torch.randperm(96, generator=g).view(3, 32)[:, :300 // bs + 2]
+    for dtype in ("float32", "bfloat16"):
+        caches, qs, wants = torch.zeros(96 * bs, G * (d + vd), dtype=DT[dtype]), [], []
+        for s, (L, n) in enumerate(zip(lens, news)):
+            q = torch.randn(L, H * d, generator=g)
+            kv = torch.cat([torch.randn(L, G * d, generator=g), torch.randn(L, G * vd, generator=g)], 1).to(DT[dtype])
+            for j in range(L):
+                caches[int(tables[s, j // bs]) * bs + j % bs] = kv[j]
+            qd = q.to(DT[dtype])
+            wants.append(ref.windowed_attention(qd.double(), kv[:, :G * d].double(), kv[:, G * d:].double(), H, G, 0.2, window)[L - n:])
+            qs.append(qd[L - n:])
+        sp = spans_varlen(news, lens)
+        sl = ref.slopes(H).float().cuda()
+        bt = tables.to(torch.int32).cuda().contiguous()
+        for kw in (PATHS[:2] if dtype == "bfloat16" else PATHS[:1]):
+            got = mixops.window_attention(torch.cat(qs).cuda(), caches.cuda(), bt, bs, sp, H, G, d, vd, 0.2, sl, window, **kw)
+            assert rel_err(got, torch.cat(wants)) < (1e-5 if dtype == "float32" else 1.2e-2), (dtype, kw)
+        # the same three sequences one token further, as a decode step (with a padding row), keys split or not
+        ctx = torch.tensor(lens + [0], dtype=torch.int32, device="cuda")
+        sp = mixops.StepSpans(4, 1, None, None, ctx)
+        qlast = torch.cat([q[-1:] for q in qs] + [torch.zeros(1, H * d, dtype=DT[dtype])]).cuda()
+        bt4 = torch.cat([bt, bt[:1]]).contiguous()
+        for kw in (PATHS if dtype == "bfloat16" else PATHS[:1]):
+            got = mixops.window_attention(qlast, caches.cuda(), bt4, bs, sp, H, G, d, vd, 0.2, sl, window, **kw)
+            assert rel_err(got[:3], torch.stack([w[-1] for w in wants])) < (1e-5 if dtype == "float32" else 1.2e-2), (dtype, kw, "decode")
+
+
+@pytest.mark.parametrize("case", [(10, 6, 3, 2, 1), (16, 4, 3, 4, 2), (9, 0, 2, 3, 1), (6, 2, 8, 1, 1), (40, 8, 6, 8, 3), (5, 3, 2, 4, 4), (2, 2, 1, 2, 1)])
+def test_router_choice_groups_and_weights(case):
+    """Softmax scores, the correction in the choice only, closed groups never chosen even when every choice score is negative,
+    identity experts reported as -1, weights renormalised and scaled."""
+    from nanovllm import mixops
+    real, ident, top, groups, keep = case
+    E = real + ident
+    g = torch.Generator().manual_seed(E * 7 + top)
+    z = torch.randn(300, E, generator=g) * 2.0
+    for shift in (0.0, -3.0):                               # -3: all choice scores negative
+        corr = torch.randn(E, generator=g) * 0.2 + shift
+        idx, w = mixops.moe_route_grouped(z.cuda(), E, top, corr.cuda(), groups, keep, real, scale=1.7)
+        chosen, want_w = ref.route(z.double(), corr.double(), top, groups, keep, 1.7)
+        want_idx = torch.where(chosen >= real, torch.full_like(chosen, -1), chosen)
+        assert torch.equal(idx.cpu().long().sort(1).values, want_idx.sort(1).values)
+        # weights: compare as a multiset per token (identity experts share the index -1)
+        assert torch.allclose(w.cpu().double().sort(1).values, want_w.sort(1).values, rtol=2e-5, atol=1e-7)
+        assert torch.allclose(w.cpu().double().sum(1), torch.full((300,), 1.7, dtype=torch.float64), rtol=1e-5)
+
+
+def device_weights(W, dtype):
+    return {k: v.to("cuda", dtype) for k, v in W.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mlp", [th.moe(), th.moe(experts=7, identity=2, top=3, groups=(3, 2), ff=16, shared=0), th.moe(experts=2, identity=2, top=2, groups=(2, 1), ff=8, shared=12),
+                                 th.moe(experts=12, identity=4, top=3, groups=(4, 2), ff=96, shared=160), th.moe(experts=1, identity=1, top=2, groups=(1, 1), ff=40, shared=0)])
+def test_routed_feed_forward(dtype, mlp):
+    """Router, grouping by expert, gated expert GEMMs, output weighting, identity experts and the shared expert against the plain
+    per-token loop; 150 tokens so that several row tiles per expert and empty experts both occur."""
+    from nanovllm.layers.moe import GroupRoutedExpertsFF
+    width = 72
+    cfg = th.config([(th.attn(), mlp)], width=width)
+    W = {k[len("l0.mlp."):]: v for k, v in th.random_weights(cfg, 5).items() if k.startswith("l0.mlp.")}
+    ff = GroupRoutedExpertsFF(width, mlp, DT[dtype], torch.device("cuda"))
+    for k, v in W.items():
+        assert ff.load(k, v.to("cuda", DT[dtype])), k
+    assert set(ff.weight_shapes(width)) == set(W)
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(150, width, generator=g)
+    h = x.to(DT[dtype])
+    got = ff.forward(h.cuda(), h.float().cuda())
+    want = ref.routed_ff({"l0.mlp." + k: v for k, v in W.items()}, "l0.mlp.", mlp, h.double())
+    if dtype == "float32":
+        assert rel_err(got, want) < 1e-5
+    else:                                                  # bf16 products: a per-token bound, so that one token with a wrong expert would show
+        per = ((got.double().cpu() - want) ** 2).mean(1).sqrt() / (want ** 2).mean(1).sqrt()
+        assert per.max().item() < 3e-2
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+# whole models through the engine
+# ---------------------------------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def checkpoints(tmp_path_factory):
+    root = tmp_path_factory.mktemp("tipetar")
+    out = {}
+    for name, cfg in (("a", th.config_a()), ("b", th.config_b()), ("c", th.config_c())):
+        W = th.random_weights(cfg, 21)
+        out[name] = (th.write_checkpoint(str(root / name), cfg, W), cfg, W)
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(checkpoints):
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = Replay(checkpoints[name][0], dtype)
+        return made[(name, dtype)]
+    yield get
+    for e in made.values():
+        e.runner.exit()
+
+
+def oracle_logits(checkpoints, name, toks):
+    _, cfg, W = checkpoints[name]
+    return ref.forward(cfg, W, toks)
+
+
+def close(got, want, dtype):
+    """fp32: every position within 3e-4 of the logits' size.  bf16: a rounded router input may swap two nearly equal experts for a
+    token, so the bound is on the median over positions, with a loose one on the whole."""
+    got, want = got.double().cpu(), want.double()
+    if dtype == "float32":
+        per = ((got - want) ** 2).mean(1).sqrt() / (want ** 2).mean(1).sqrt()
+        return per.max().item() < TOL[dtype]
+    per = ((got - want) ** 2).mean(1).sqrt() / (want ** 2).mean(1).sqrt()
+    return per.median().item() < 0.04 and rel_err(got, want) < 0.2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_whole_prompt_and_first_tokens(engines, checkpoints, name, dtype):
+    e = engines(name, dtype)
+    vocab = checkpoints[name][1]["vocab"]
+    for i, n in enumerate((1, 2, 17, 150)):
+        toks = th.tokens(n, vocab, i)
+        got = e.step([("p", toks)])["p"]
+        e.end("p")
+        assert close(got, oracle_logits(checkpoints, name, toks), dtype), n
+
+
+def test_layers_one_by_one(engines, checkpoints):
+    """The residual stream after every layer, in 32 bits, against the plain implementation's."""
+    e = engines("a", "float32")
+    _, cfg, W = checkpoints["a"]
+    toks = th.tokens(60, cfg["vocab"], 3)
+    want = []
+    ref.forward(cfg, W, toks, want)
+    taps = []
+    model = e.runner.model
+    plain = type(model).__call__
+    type(model).__call__ = lambda self, ids, pos: type(model).forward(self, ids, pos, taps)
+    try:
+        e.step([("p", toks)])
+    finally:
+        type(model).__call__ = plain
+        e.end("p")
+    assert len(taps) == len(want)
+    for i, (a, b) in enumerate(zip(taps, want)):
+        assert rel_err(a, b) < 2e-5, i
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_long_decoding_matches_the_prompt_path(engines, checkpoints, name, dtype):
+    """One prompt token, then 170 tokens one by one through the decode graphs, across ten pages and past every window."""
+    e = engines(name, dtype)
+    toks = th.tokens(171, checkpoints[name][1]["vocab"], 5)
+    want = oracle_logits(checkpoints, name, toks)
+    got = [e.step([("d", toks[:1])])["d"]]
+    for t in toks[1:]:
+        got.append(e.step([("d", [t])])["d"])
+    e.end("d")
+    got = torch.cat(got)
+    assert close(got, want, dtype)
+    assert close(got[-20:], want[-20:], dtype)               # no drift at the far end
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_portions_of_many_sizes(engines, checkpoints, name, dtype):
+    e = engines(name, dtype)
+    cuts = (2, 3, 2, 31, 16, 2, 1, 1, 48, 15, 1, 5, 33, 64, 2, 7)
+    toks = th.tokens(sum(cuts), checkpoints[name][1]["vocab"], 6)
+    got, at = [], 0
+    for n in cuts:
+        got.append(e.step([("c", toks[at:at + n])])["c"])
+        at += n
+    e.end("c")
+    assert close(torch.cat(got), oracle_logits(checkpoints, name, toks), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "c"])
+def test_unequal_requests_in_one_batch_and_reused_pages(engines, checkpoints, name, dtype):
+    """Four requests of unequal length, portions beside single tokens; two of them end early and a fifth and sixth take over
+    their pages while the others go on.  Every request must come out as if it had run alone."""
+    e = engines(name, dtype)
+    vocab = checkpoints[name][1]["vocab"]
+    T = {k: th.tokens(n, vocab, 10 + i) for i, (k, n) in enumerate(dict(a=90, b=37, c=9, d=140, e=70, f=44).items())}
+    plan = [
+        [("a", 40), ("b", 2)], [("a", 1), ("b", 30), ("c", 9)], [("a", 1), ("b", 1), ("d", 64)], [("a", 1), ("b", 1), ("d", 1)],
+        [("a", 17), ("b", 3), ("d", 2)], [("a", 1), ("d", 1)], [("a", 29), ("d", 72)],
+        [("e", 33), ("f", 1), ("d", 0)], [("e", 1), ("f", 43)], [("e", 36)],
+    ]
+    got = {k: [] for k in T}
+    at = {k: 0 for k in T}
+    ended = set()
+    for step in plan:
+        entries = [(k, T[k][at[k]:at[k] + n]) for k, n in step if n]
+        for k, n in step:
+            at[k] += n
+        for k, lg in e.step(entries).items():
+            got[k].append(lg)
+        for k in T:
+            if at[k] == len(T[k]) and k in e.live and k not in ended:
+                e.end(k)
+                ended.add(k)
+    assert ended == set(T)
+    for k in T:
+        assert close(torch.cat(got[k]), oracle_logits(checkpoints, name, T[k]), dtype), k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_of_64_tokens_and_windows_at_the_tile_edge(checkpoints, dtype):
+    """Pages as long as the attention kernel's key tile, windows of 63, 64, 65 and 130 keys, a prompt in portions that end beside page
+    borders, decoding over a page border, and a second request arriving in the middle."""
+    e = Replay(checkpoints["c"][0], dtype, pool_tokens=768, block=64, seqs=3)
+    vocab = checkpoints["c"][1]["vocab"]
+    a, b = th.tokens(333, vocab, 81), th.tokens(90, vocab, 82)
+    got = {"a": [], "b": []}
+    at = {"a": 0, "b": 0}
+    for step in ([("a", 63)], [("a", 2)], [("a", 64), ("b", 1)], [("a", 1), ("b", 70)], [("a", 130), ("b", 1)], [("a", 1), ("b", 18)], [("a", 60)],
+                 *[[("a", 1)] for _ in range(12)]):
+        entries = [(k, (a if k == "a" else b)[at[k]:at[k] + n]) for k, n in step]
+        for k, n in step:
+            at[k] += n
+        for k, lg in e.step(entries).items():
+            got[k].append(lg)
+    e.runner.exit()
+    assert at == {"a": 333, "b": 90}
+    for k, toks in (("a", a), ("b", b)):
+        assert close(torch.cat(got[k]), oracle_logits(checkpoints, "c", toks), dtype), k
+
+
+def test_batch_does_not_change_a_request_beyond_rounding(engines, checkpoints):
+    e = engines("a", "float32")
+    vocab = checkpoints["a"][1]["vocab"]
+    x, y = th.tokens(50, vocab, 30), th.tokens(21, vocab, 31)
+    alone = e.step([("x", x)])["x"]
+    e.end("x")
+    both = e.step([("y", y), ("x", x)])["x"]
+    e.end("x"), e.end("y")
+    assert rel_err(both, alone) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(checkpoints, dtype):
+    """LLM.generate on a checkpoint without a tokenizer: scheduler, block manager with its prefix cache, decode graphs, sampler.
+    Teacher-forced against the plain implementation: each generated token is its argmax, or loses to it by less than the format's
+    rounding.  Two prompts share their first 48 tokens (three pages), so the second one starts from cached pages."""
+    from nanovllm import LLM, SamplingParams
+    path, cfg, W = checkpoints["a"]
+    llm = LLM(path, dtype=dtype, max_num_seqs=3, max_model_len=256, max_num_batched_tokens=96, kvcache_block_size=16,
+              num_kvcache_blocks=32, gpu_memory_utilization=0.5)
+    prompts = [th.tokens(n, cfg["vocab"], 40 + i) for i, n in enumerate((5, 61, 1, 100, 18))]      # more requests than slots, chunked prompts
+    prompts.append(prompts[1][:48] + th.tokens(9, cfg["vocab"], 99))
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True), use_tqdm=False)
+    llm.exit()
+    assert [len(o["token_ids"]) for o in outs] == [24] * len(prompts)
+    tol = 1e-3 if dtype == "float32" else 0.15
+    loose = []                       # bf16: a token whose top-1 expert is a near tie may take the other one, which moves its logits more
+    for p, o in zip(prompts, outs):
+        seq = p + o["token_ids"]
+        lg = ref.forward(cfg, W, seq[:-1])
+        for i, tok in enumerate(o["token_ids"]):
+            row = lg[len(p) - 1 + i]
+            gap = (row.max() - row[tok]).item() / row.std().item()
+            if gap > tol:
+                loose.append((len(p), i, gap))
+    assert not loose if dtype == "float32" else (len(loose) <= 3 and all(g < 0.5 for _, _, g in loose)), loose
+
+
+def test_replay_command_line(checkpoints, tmp_path):
+    """bin/trace_run end to end: JSON steps on stdin, logits files and 'done' lines out."""
+    import json
+    import os
+    import subprocess
+    import numpy as np
+    path, cfg, W = checkpoints["b"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = th.tokens(40, cfg["vocab"], 50)
+    steps = [{"step": 0, "entries": [{"id": "q", "tokens": toks[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "q", "tokens": toks[30:31], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "q", "tokens": toks[31:32], "want": [0]}, {"id": "r", "tokens": toks[:3], "want": [2]}], "end": ["r"]},
+             {"step": 3, "entries": [{"id": "q", "tokens": toks[32:], "want": [7]}], "end": ["q"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    want = ref.forward(cfg, W, toks)
+    rd = lambda i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"]))
+    assert not (out / "1.f32").exists()
+    assert rel_err(rd(0), want[[0, 29]]) < 3e-4 and rel_err(rd(3), want[[39]]) < 3e-4
+    assert rel_err(rd(2), torch.stack([want[31], want[2]])) < 3e-4
