@@ -541,7 +541,16 @@ def main():
                     help="instead of the headline workload: prefill / decode throughput of the Tafopel hybrid decoder beside Qwen3 at equal "
                          "size, with a per-kernel roofline table (profiles/hybrid_bench.py); one GPU")
     ap.add_argument("--hybrid-sizes", default="w1024,w2048")
+    ap.add_argument("--windowed", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the Tipetar decoder (windowed attention, group-routed "
+                         "experts) beside Tafopel and Qwen3 at equal size, with a per-kernel roofline table (profiles/window_bench.py); one GPU")
+    ap.add_argument("--windowed-sizes", default="w1024,w2048")
     args = ap.parse_args()
+    if args.windowed:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
+        import window_bench
+        window_bench.main(["--sizes", args.windowed_sizes])
+        return
     if args.hybrid:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
         import hybrid_bench

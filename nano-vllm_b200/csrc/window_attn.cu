@@ -207,32 +207,41 @@ __device__ __forceinline__ void wm_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float wm_ex2(float x) {       // 2^x on the special-function unit; -inf -> 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t wm_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int DK, int DV>
+// KS (single-token steps with at most 16 query heads per key/value head): the CTA's 16 rows are shared by its four warps, each
+// of which takes 16 of a tile's 64 keys with its own running (max, sum, O); the four are merged through shared memory at the end.
+template <int DK, int DV, bool KS, bool QREG>
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache, int row_elems, int v_off,
-    const int32_t* __restrict__ block_tables, int bt_stride, int block_size, const int32_t* __restrict__ cu_q,
+    const int32_t* __restrict__ block_tables, int bt_stride, int block_size, int bs_shift, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, const float* __restrict__ slopes, int window,
     __nv_bfloat16* __restrict__ out, int H, int G, float scale, int splits, float* __restrict__ part) {
     B200_PDL_SYNC();
-    constexpr int KS = DK + 8, VS = DV + 8;               // row strides: 16-byte multiples, odd in 16-byte units (conflict-free ldmatrix)
+    constexpr int KSTR = DK + 8, VSTR = DV + 8;           // row strides: 16-byte multiples, odd in 16-byte units (conflict-free ldmatrix)
+    constexpr int BM = KS ? 16 : WM_BM;                   // rows of the CTA
+    constexpr int WK = KS ? 16 : WM_BN;                   // keys of a tile one warp multiplies
     extern __shared__ __align__(16) unsigned char wm_smem[];
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);       // [64][KS]
-    __nv_bfloat16* Ks = Qs + WM_BM * KS;                                 // [2][64][KS]
-    __nv_bfloat16* Vs = Ks + 2 * WM_BN * KS;                             // [2][64][VS]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);       // [BM][KSTR]
+    __nv_bfloat16* Ks = Qs + BM * KSTR;                                  // [2][64][KSTR]
+    __nv_bfloat16* Vs = Ks + 2 * WM_BN * KSTR;                           // [2][64][VSTR]
     const int s = blockIdx.y, rep = H / G;
     const int g = blockIdx.z / splits, split = blockIdx.z - g * splits;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     const int nrows = sp.qlen * rep;
-    const int row0 = (gridDim.x - 1 - blockIdx.x) * WM_BM;               // the last rows of a portion see the most keys: launched first
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * BM;                  // the last rows of a portion see the most keys: launched first
     if (row0 >= nrows) return;
     const int first = sp.klen - sp.qlen;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t4 = lane & 3;
-    const int i_lo = row0 / rep, i_hi = min(sp.qlen - 1, (row0 + WM_BM - 1) / rep);
+    const int i_lo = row0 / rep, i_hi = min(sp.qlen - 1, (row0 + BM - 1) / rep);
     const int kmax = first + i_hi + 1;
     const int kmin = window > 0 ? max(0, first + i_lo - window + 1) : 0;
     int t_lo = kmin / WM_BN, t_hi = (kmax + WM_BN - 1) / WM_BN;          // key tiles [t_lo, t_hi)
@@ -244,29 +253,43 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     }
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
 
-    auto load_tile = [&](int buf, int t) {
+    // a tile's rows: eight lanes copy one cache row (128 contiguous bytes per step), sixteen rows per pass.  The page numbers of a
+    // tile are looked up one tile ahead of its copies, so that the table read never stands between a warp and its next MMAs.
+    const int lr = tid >> 3, lc = tid & 7;
+    auto lookup = [&](int t, int (&pg)[WM_BN / 16]) {
+#pragma unroll
+        for (int p = 0; p < WM_BN / 16; ++p) {
+            const int j = t * WM_BN + p * 16 + lr;
+            pg[p] = (t < t_hi && j < kmax) ? bt[bs_shift >= 0 ? j >> bs_shift : j / block_size] : -1;
+        }
+    };
+    auto load_tile = [&](int buf, int t, const int (&pg)[WM_BN / 16]) {
         const int j0 = t * WM_BN;
-        __nv_bfloat16* kd = Ks + buf * WM_BN * KS;
-        __nv_bfloat16* vd = Vs + buf * WM_BN * VS;
+        __nv_bfloat16* kd = Ks + buf * WM_BN * KSTR;
+        __nv_bfloat16* vd = Vs + buf * WM_BN * VSTR;
         constexpr int KC = DK / 8, VC = DV / 8;
-        for (int e = tid; e < WM_BN * (KC + VC); e += 128) {
-            const int r = e / (KC + VC), c = e - r * (KC + VC);
+#pragma unroll
+        for (int p = 0; p < WM_BN / 16; ++p) {
+            const int r = p * 16 + lr;
             const int j = j0 + r;
-            const bool ok = j < kmax;
-            const __nv_bfloat16* src = cache;
-            if (ok) {
-                const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
-                src = cache + slot * row_elems + (c < KC ? g * DK + c * 8 : v_off + g * DV + (c - KC) * 8);
-            }
-            const uint32_t dst = c < KC ? smem_u32(kd + r * KS + c * 8) : smem_u32(vd + r * VS + (c - KC) * 8);
-            wm_cp16(dst, src, ok ? 16 : 0);
+            const bool ok = pg[p] >= 0;
+            const int in_page = bs_shift >= 0 ? j & (block_size - 1) : j % block_size;
+            const __nv_bfloat16* src = ok ? cache + ((int64_t)pg[p] * block_size + in_page) * row_elems : cache;
+            const int nb = ok ? 16 : 0;
+#pragma unroll
+            for (int c = lc; c < KC; c += 8) wm_cp16(smem_u32(kd + r * KSTR + c * 8), ok ? src + g * DK + c * 8 : src, nb);
+#pragma unroll
+            for (int c = lc; c < VC; c += 8) wm_cp16(smem_u32(vd + r * VSTR + c * 8), ok ? src + v_off + g * DV + c * 8 : src, nb);
         }
         wm_commit();
     };
-    if (t_lo < t_hi) load_tile(0, t_lo);
+    int pg[WM_BN / 16];
+    lookup(t_lo, pg);
+    if (t_lo < t_hi) load_tile(0, t_lo, pg);
+    lookup(t_lo + 1, pg);
 
     // queries of this CTA's rows (plain loads; visible after the loop's first barrier)
-    for (int e = tid; e < WM_BM * (DK / 8); e += 128) {
+    for (int e = tid; e < BM * (DK / 8); e += 128) {
         const int r = e / (DK / 8), c = e - r * (DK / 8);
         const int rr = row0 + r;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -274,27 +297,38 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             const int i = rr / rep, h = g * rep + (rr - i * rep);
             v = *reinterpret_cast<const uint4*>(q + (int64_t)(sp.q0 + i) * q_stride + (int64_t)h * DK + c * 8);
         }
-        *reinterpret_cast<uint4*>(Qs + r * KS + c * 8) = v;
+        *reinterpret_cast<uint4*>(Qs + r * KSTR + c * 8) = v;
     }
 
-    // this thread's two rows: warp * 16 + gq and + 8
+    // this thread's two rows: (warp * 16 +) gq and + 8
+    const int wrow = KS ? 0 : warp * 16;                  // first row of this warp within the CTA
+    const int wkey = KS ? warp * 16 : 0;                  // first key of this warp within a tile
     int pos_r[2];
     float slope2[2];
     bool live[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-        const int rr = row0 + warp * 16 + gq + 8 * hh;
+        const int rr = row0 + wrow + gq + 8 * hh;
         live[hh] = rr < nrows;
         const int i = live[hh] ? rr / rep : 0;
         pos_r[hh] = first + i;
         slope2[hh] = (live[hh] && slopes) ? slopes[g * rep + (rr - i * rep)] * WM_LOG2E : 0.f;
     }
-    // keys any row of this warp sees: [w_lo, w_hi]
-    const int wr0 = row0 + warp * 16, wr1 = min(nrows - 1, wr0 + 15);
+    // keys any row of this warp sees: [w_lo, w_hi]; keys every row of this warp sees: [f_lo, f_hi] (empty unless all 16 rows are live)
+    const int wr0 = row0 + wrow, wr1 = min(nrows - 1, wr0 + 15);
     const int w_hi = wr0 < nrows ? first + wr1 / rep : -1;
     const int w_lo = window > 0 ? max(0, first + wr0 / rep - window + 1) : 0;
+    const int f_hi = wr0 + 15 < nrows ? first + wr0 / rep : -1;
+    const int f_lo = window > 0 ? max(0, first + wr1 / rep - window + 1) : 0;
     const float scale2 = scale * WM_LOG2E;
 
+    __syncthreads();                                                     // the queries are staged: keep this warp's fragments in registers
+    const uint32_t a_base = smem_u32(Qs + (wrow + (lane & 15)) * KSTR + ((lane >> 4) << 3));
+    uint32_t qf[QREG ? DK / 16 : 1][4];
+    if constexpr (QREG) {
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk) wm_ldsm(a_base + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DV / 8][4];
 #pragma unroll
@@ -303,62 +337,85 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     for (int t = t_lo; t < t_hi; ++t) {
         const int buf = (t - t_lo) & 1;
         if (t + 1 < t_hi) {
-            load_tile(buf ^ 1, t + 1);
+            load_tile(buf ^ 1, t + 1, pg);
+            lookup(t + 2, pg);
             wm_wait<1>();
         } else {
             wm_wait<0>();
         }
         __syncthreads();
-        const int j0 = t * WM_BN;
-        if (w_hi >= j0 && w_lo < j0 + WM_BN) {                           // warp-uniform: some row of this warp sees some key of the tile
-            const __nv_bfloat16* kt = Ks + buf * WM_BN * KS;
-            const __nv_bfloat16* vt = Vs + buf * WM_BN * VS;
-            float sc[WM_BN / 8][4];
+        const int j0 = t * WM_BN + wkey;                                 // first key this warp multiplies
+        if (w_hi >= j0 && w_lo < j0 + WK) {                              // warp-uniform: some row of this warp sees some key of its share
+            const __nv_bfloat16* kt = Ks + buf * WM_BN * KSTR + wkey * KSTR;
+            const __nv_bfloat16* vt = Vs + buf * WM_BN * VSTR + wkey * VSTR;
+            float sc[WK / 8][4];
 #pragma unroll
-            for (int n = 0; n < WM_BN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-            const uint32_t a_base = smem_u32(Qs + (warp * 16 + (lane & 15)) * KS + ((lane >> 4) << 3));
-            const uint32_t b_base = smem_u32(kt + ((lane & 7) + ((lane >> 4) << 3)) * KS + (((lane >> 3) & 1) << 3));
+            for (int n = 0; n < WK / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+            const uint32_t b_base = smem_u32(kt + ((lane & 7) + ((lane >> 4) << 3)) * KSTR + (((lane >> 3) & 1) << 3));
+            {   // S = Q K^T; the next key fragment is loaded before the current one is multiplied
+                constexpr int NP = WK / 16, STEPS = (DK / 16) * NP;
+                uint32_t bc[4], bn[4] = {0, 0, 0, 0}, ac[4] = {0, 0, 0, 0};
+                wm_ldsm(b_base, bc[0], bc[1], bc[2], bc[3]);
 #pragma unroll
-            for (int kk = 0; kk < DK; kk += 16) {
-                uint32_t a0, a1, a2, a3;
-                wm_ldsm(a_base + kk * 2, a0, a1, a2, a3);
+                for (int st = 0; st < STEPS; ++st) {
+                    const int kk = st / NP, np = st % NP;
+                    if (!QREG && np == 0) wm_ldsm(a_base + kk * 32, ac[0], ac[1], ac[2], ac[3]);
+                    if (st + 1 < STEPS) {
+                        const int kn = (st + 1) / NP, nn = (st + 1) % NP;
+                        wm_ldsm(b_base + (nn * 16 * KSTR + kn * 16) * 2, bn[0], bn[1], bn[2], bn[3]);
+                    }
+                    if constexpr (QREG) {
+                        wm_mma(sc[2 * np], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], bc[0], bc[1]);
+                        wm_mma(sc[2 * np + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], bc[2], bc[3]);
+                    } else {
+                        wm_mma(sc[2 * np], ac[0], ac[1], ac[2], ac[3], bc[0], bc[1]);
+                        wm_mma(sc[2 * np + 1], ac[0], ac[1], ac[2], ac[3], bc[2], bc[3]);
+                    }
 #pragma unroll
-                for (int np = 0; np < WM_BN / 16; ++np) {
-                    uint32_t b0, b1, b2, b3;
-                    wm_ldsm(b_base + (np * 16 * KS + kk) * 2, b0, b1, b2, b3);
-                    wm_mma(sc[2 * np], a0, a1, a2, a3, b0, b1);
-                    wm_mma(sc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                    for (int x = 0; x < 4; ++x) bc[x] = bn[x];
                 }
             }
-            // scale, bias, mask; running maximum
+            // scale, bias, mask; running maximum.  Inside the window of every row of the warp no mask is needed: two FMAs per score.
             float m_new[2] = {m_run[0], m_run[1]};
+            if (j0 + WK - 1 <= f_hi && j0 >= f_lo) {
+                const float base0 = -slope2[0] * (float)(pos_r[0] - j0 - 2 * t4), base1 = -slope2[1] * (float)(pos_r[1] - j0 - 2 * t4);
 #pragma unroll
-            for (int n = 0; n < WM_BN / 8; ++n)
+                for (int n = 0; n < WK / 8; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int hh = e >> 1;
-                    const int j = j0 + n * 8 + 2 * t4 + (e & 1);
-                    const int dist = pos_r[hh] - j;
-                    const bool ok = live[hh] && dist >= 0 && (window <= 0 || dist < window);
-                    const float v = ok ? fmaf(sc[n][e], scale2, -slope2[hh] * (float)dist) : -INFINITY;
-                    sc[n][e] = v;
-                    m_new[hh] = fmaxf(m_new[hh], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const int hh = e >> 1;
+                        const float v = fmaf(sc[n][e], scale2, fmaf(slope2[hh], (float)(n * 8 + (e & 1)), hh ? base1 : base0));
+                        sc[n][e] = v;
+                        m_new[hh] = fmaxf(m_new[hh], v);
+                    }
+            } else {
+#pragma unroll
+                for (int n = 0; n < WK / 8; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int hh = e >> 1;
+                        const int dist = pos_r[hh] - (j0 + n * 8 + 2 * t4 + (e & 1));
+                        const bool ok = live[hh] && dist >= 0 && (window <= 0 || dist < window);
+                        const float v = ok ? fmaf(sc[n][e], scale2, -slope2[hh] * (float)dist) : -INFINITY;
+                        sc[n][e] = v;
+                        m_new[hh] = fmaxf(m_new[hh], v);
+                    }
+            }
             float alpha[2], m_use[2];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 m_new[hh] = fmaxf(m_new[hh], __shfl_xor_sync(0xffffffffu, m_new[hh], 1));
                 m_new[hh] = fmaxf(m_new[hh], __shfl_xor_sync(0xffffffffu, m_new[hh], 2));
                 m_use[hh] = m_new[hh] == -INFINITY ? 0.f : m_new[hh];    // a row that has seen nothing yet
-                alpha[hh] = exp2f(m_run[hh] - m_use[hh]);
+                alpha[hh] = wm_ex2(m_run[hh] - m_use[hh]);
                 m_run[hh] = m_new[hh];
                 l_run[hh] *= alpha[hh];
             }
 #pragma unroll
-            for (int n = 0; n < WM_BN / 8; ++n)
+            for (int n = 0; n < WK / 8; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p = exp2f(sc[n][e] - m_use[e >> 1]);
+                    const float p = wm_ex2(sc[n][e] - m_use[e >> 1]);
                     sc[n][e] = p;
                     l_run[e >> 1] += p;
                 }
@@ -370,17 +427,28 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                 o[n][3] *= alpha[1];
             }
             // O += P V: P from the S fragments, V through transposing loads
-            const uint32_t v_base = smem_u32(vt + ((lane & 7) + (((lane >> 3) & 1) << 3)) * VS + ((lane >> 4) << 3));
+            const uint32_t v_base = smem_u32(vt + ((lane & 7) + (((lane >> 3) & 1) << 3)) * VSTR + ((lane >> 4) << 3));
+            {
+                constexpr int NP = DV / 16, STEPS = (WK / 16) * NP;
+                uint32_t bc[4], bn[4] = {0, 0, 0, 0}, pa[4] = {0, 0, 0, 0};
+                wm_ldsm_t(v_base, bc[0], bc[1], bc[2], bc[3]);
 #pragma unroll
-            for (int kk = 0; kk < WM_BN / 16; ++kk) {
-                const uint32_t a0 = wm_pack(sc[2 * kk][0], sc[2 * kk][1]), a1 = wm_pack(sc[2 * kk][2], sc[2 * kk][3]);
-                const uint32_t a2 = wm_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), a3 = wm_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+                for (int st = 0; st < STEPS; ++st) {
+                    const int kk = st / NP, np = st % NP;
+                    if (np == 0) {
+                        pa[0] = wm_pack(sc[2 * kk][0], sc[2 * kk][1]);
+                        pa[1] = wm_pack(sc[2 * kk][2], sc[2 * kk][3]);
+                        pa[2] = wm_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                        pa[3] = wm_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+                    }
+                    if (st + 1 < STEPS) {
+                        const int kn = (st + 1) / NP, nn = (st + 1) % NP;
+                        wm_ldsm_t(v_base + (kn * 16 * VSTR + nn * 16) * 2, bn[0], bn[1], bn[2], bn[3]);
+                    }
+                    wm_mma(o[2 * np], pa[0], pa[1], pa[2], pa[3], bc[0], bc[1]);
+                    wm_mma(o[2 * np + 1], pa[0], pa[1], pa[2], pa[3], bc[2], bc[3]);
 #pragma unroll
-                for (int np = 0; np < DV / 16; ++np) {
-                    uint32_t b0, b1, b2, b3;
-                    wm_ldsm_t(v_base + (kk * 16 * VS + np * 16) * 2, b0, b1, b2, b3);
-                    wm_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
-                    wm_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                    for (int x = 0; x < 4; ++x) bc[x] = bn[x];
                 }
             }
         }
@@ -391,6 +459,55 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
     }
+    if constexpr (KS) {
+        // merge the four warps' partials of the 16 rows through shared memory (the value buffers: all tiles are consumed)
+        float* scr = reinterpret_cast<float*>(Vs);                       // [4][16][DV + 2]: max, sum, O
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float* pr = scr + ((size_t)warp * 16 + gq + 8 * hh) * (DV + 2);
+            if (t4 == 0) {
+                pr[0] = m_run[hh];
+                pr[1] = l_run[hh];
+            }
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) {
+                pr[2 + n * 8 + 2 * t4] = o[n][2 * hh];
+                pr[2 + n * 8 + 2 * t4 + 1] = o[n][2 * hh + 1];
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < 16 * DV; e += 128) {
+            const int r = e / DV, c = e - r * DV;
+            const int rr = row0 + r;
+            if (rr >= nrows) continue;
+            const float* pr = scr + (size_t)r * (DV + 2);
+            constexpr int WSTEP = 16 * (DV + 2);
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, pr[w * WSTEP]);
+            float L = 0.f, a = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = pr[w * WSTEP];
+                if (mw != -INFINITY) {
+                    const float f = exp2f(mw - M);
+                    L = fmaf(pr[w * WSTEP + 1], f, L);
+                    a = fmaf(pr[w * WSTEP + 2 + c], f, a);
+                }
+            }
+            const int i = rr / rep, h = g * rep + (rr - i * rep);
+            if (splits > 1) {
+                float* pp = part + (((int64_t)s * splits + split) * H + h) * (DV + 2);
+                if (c == 0) {
+                    pp[0] = M;
+                    pp[1] = L;
+                }
+                pp[2 + c] = a;
+            } else {
+                out[((int64_t)(sp.q0 + i) * H + h) * DV + c] = __float2bfloat16_rn(a / L);
+            }
+        }
+    } else {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int rr = row0 + warp * 16 + gq + 8 * hh;
@@ -414,6 +531,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             for (int n = 0; n < DV / 8; ++n)
                 *reinterpret_cast<uint32_t*>(op + n * 8 + 2 * t4) = wm_pack(o[n][2 * hh] * inv, o[n][2 * hh + 1] * inv);
         }
+    }
     }
 }
 
@@ -440,23 +558,40 @@ __global__ void window_merge_kernel(const float* __restrict__ part, const int32_
     }
 }
 
+template <int DK, int DV, bool KS, bool QREG>
+int launch_window_mma_as(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
+                         int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
+                         const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
+                         float* part, cudaStream_t stream) {
+    using bf = __nv_bfloat16;
+    constexpr int BM = KS ? 16 : WM_BM;
+    const size_t smem = sizeof(bf) * ((size_t)BM * (DK + 8) + 2 * (size_t)WM_BN * (DK + 8) + 2 * (size_t)WM_BN * (DV + 8));
+    int rc = wa_ensure_smem(window_attn_mma_kernel<DK, DV, KS, QREG>, smem);
+    if (rc != B200_OK) return rc;
+    int bs_shift = -1;
+    if ((block_size & (block_size - 1)) == 0)
+        for (bs_shift = 0; (1 << bs_shift) < block_size; ++bs_shift) {}
+    dim3 grid((max_q * (H / G) + BM - 1) / BM, num_seqs, G * splits);
+    B200_LAUNCH((window_attn_mma_kernel<DK, DV, KS, QREG>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
+                static_cast<const bf*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, bs_shift, cu_q, cu_k, ctx_lens,
+                slopes, window, static_cast<bf*>(out), H, G, scale, splits, part);
+    rc = b200_launch_status(nullptr);
+    if (rc != B200_OK || splits <= 1) return rc;
+    B200_LAUNCH((window_merge_kernel), dim3(num_seqs, H), DV < 64 ? 32 : 64, 0, stream, part, ctx_lens, static_cast<bf*>(out), H, DV, splits);
+    return b200_launch_status(nullptr);
+}
+
 template <int DK, int DV>
 int launch_window_mma(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
                       int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
                       const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
                       float* part, cudaStream_t stream) {
-    using bf = __nv_bfloat16;
-    const size_t smem = sizeof(bf) * ((size_t)WM_BM * (DK + 8) + 2 * (size_t)WM_BN * (DK + 8) + 2 * (size_t)WM_BN * (DV + 8));
-    int rc = wa_ensure_smem(window_attn_mma_kernel<DK, DV>, smem);
-    if (rc != B200_OK) return rc;
-    dim3 grid((max_q * (H / G) + WM_BM - 1) / WM_BM, num_seqs, G * splits);
-    B200_LAUNCH((window_attn_mma_kernel<DK, DV>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
-                static_cast<const bf*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens, slopes,
-                window, static_cast<bf*>(out), H, G, scale, splits, part);
-    rc = b200_launch_status(nullptr);
-    if (rc != B200_OK || splits <= 1) return rc;
-    B200_LAUNCH((window_merge_kernel), dim3(num_seqs, H), DV < 64 ? 32 : 64, 0, stream, part, ctx_lens, static_cast<bf*>(out), H, DV, splits);
-    return b200_launch_status(nullptr);
+    if (cu_q == nullptr && H / G <= 16)                   // single-token step: the four warps share every key tile
+        return launch_window_mma_as<DK, DV, true, true>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                                  ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
+    // row-tiled form: query fragments are re-read from shared memory per key tile (measured faster than 32 more live registers)
+    return launch_window_mma_as<DK, DV, false, false>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                                      ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
 }
 
 }  // namespace

@@ -46,13 +46,22 @@ SIZES = {
 }
 
 
+EXTRA_KINDS: dict = {}          # kind -> function(size name) -> model configuration; other benches register their designs here
+
+
 def make_engine(kind: str, size: str, max_seqs: int, max_tokens: int, max_len: int):
     from nanovllm.config import Config
     from nanovllm.engine.model_runner import ModelRunner
     from nanovllm.engine.scheduler import Scheduler
     from nanovllm.engine.sequence import Sequence
-    width, layers, heads, kv_rank, experts, top = SIZES[size]
-    if kind == "tafopel":
+    if kind in EXTRA_KINDS:
+        hf = EXTRA_KINDS[kind](size)
+        width = hf.hidden_size
+    else:
+        width, layers, heads, kv_rank, experts, top = SIZES[size]
+    if kind in EXTRA_KINDS:
+        pass
+    elif kind == "tafopel":
         from nanovllm.models.tafopel import TafopelConfig
         hf = TafopelConfig(tafopel_config(width, layers, heads, kv_rank, experts, top))
     else:
