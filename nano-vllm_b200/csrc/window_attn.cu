@@ -55,6 +55,47 @@ __global__ void __launch_bounds__(256) qk_norm_store_kernel(T* __restrict__ qkv,
     for (int c = threadIdx.x; c < v_cols; c += blockDim.x) dst[k_cols + c] = k[k_cols + c];
 }
 
+// bf16 rows whose three parts are multiples of 8 columns: 128-bit accesses, 8 columns per thread and step
+__global__ void __launch_bounds__(256) qk_norm_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, int64_t stride, int q_cols, int k_cols,
+                                                                int v_cols, const __nv_bfloat16* __restrict__ wq,
+                                                                const __nv_bfloat16* __restrict__ wk, const int32_t* __restrict__ slots,
+                                                                __nv_bfloat16* __restrict__ cache, float eps) {
+    B200_PDL_SYNC();
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    __nv_bfloat16* x = qkv + (int64_t)t * stride;
+    auto sum_sq = [&](const __nv_bfloat16* p, int cols) {
+        float q = 0.f;
+        for (int c = threadIdx.x * 8; c < cols; c += 256 * 8) {
+            float f[8];
+            unpack8(*reinterpret_cast<const uint4*>(p + c), f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) q = fmaf(f[e], f[e], q);
+        }
+        return block_sum(q, red);
+    };
+    auto scaled = [&](const __nv_bfloat16* p, const __nv_bfloat16* w, float rstd, int c) {
+        float f[8], g[8];
+        unpack8(*reinterpret_cast<const uint4*>(p + c), f);
+        unpack8(*reinterpret_cast<const uint4*>(w + c), g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = f[e] * rstd * g[e];
+        return pack8(f);
+    };
+    if (wq != nullptr) {
+        const float rstd = 1.0f / sqrtf(sum_sq(x, q_cols) / (float)q_cols + eps);
+        for (int c = threadIdx.x * 8; c < q_cols; c += 256 * 8) *reinterpret_cast<uint4*>(x + c) = scaled(x, wq, rstd, c);
+    }
+    if (k_cols + v_cols == 0) return;
+    const int slot = slots[t];
+    if (slot < 0) return;                                  // block-uniform
+    __nv_bfloat16* dst = cache + (int64_t)slot * (k_cols + v_cols);
+    const __nv_bfloat16* k = x + q_cols;
+    const float rstd = wk ? 1.0f / sqrtf(sum_sq(k, k_cols) / (float)k_cols + eps) : 1.0f;
+    for (int c = threadIdx.x * 8; c < k_cols + v_cols; c += 256 * 8)
+        *reinterpret_cast<uint4*>(dst + c) = (c < k_cols && wk) ? scaled(k, wk, rstd, c) : *reinterpret_cast<const uint4*>(k + c);
+}
+
 // One warp per (token, head-in-group) pair; a CTA covers WA_WARPS consecutive pairs of one sequence and one key/value head.
 // OACC = ceil(vdim / 32): output accumulators per lane.
 template <typename T, int OACC>
@@ -187,7 +228,7 @@ int launch_window_fma(const void* q, int64_t q_stride, const void* cache, int ro
 // Tiles start at multiples of 64 keys; rows past the last visible key are zero-filled (never read: their page may be absent).
 // splits > 1 (single-token steps): blockIdx.z also names a share of the key tiles and the CTA leaves unnormalised partials.
 // ---------------------------------------------------------------------------------------------------------------------------
-constexpr int WM_BM = 64, WM_BN = 64;
+constexpr int WM_BM = 64;
 constexpr float WM_LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void wm_cp16(uint32_t dst, const void* src, int bytes) {
@@ -219,20 +260,21 @@ __device__ __forceinline__ uint32_t wm_pack(float lo, float hi) {
 
 // KS (single-token steps with at most 16 query heads per key/value head): the CTA's 16 rows are shared by its four warps, each
 // of which takes 16 of a tile's 64 keys with its own running (max, sum, O); the four are merged through shared memory at the end.
-template <int DK, int DV, bool KS, bool QREG>
+template <int DK, int DV, bool KS, bool QREG, int BN>
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache, int row_elems, int v_off,
     const int32_t* __restrict__ block_tables, int bt_stride, int block_size, int bs_shift, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, const float* __restrict__ slopes, int window,
     __nv_bfloat16* __restrict__ out, int H, int G, float scale, int splits, float* __restrict__ part) {
+    static_assert(!KS || BN == 64, "the key-sharing form shares out 64-key tiles");
     B200_PDL_SYNC();
     constexpr int KSTR = DK + 8, VSTR = DV + 8;           // row strides: 16-byte multiples, odd in 16-byte units (conflict-free ldmatrix)
     constexpr int BM = KS ? 16 : WM_BM;                   // rows of the CTA
-    constexpr int WK = KS ? 16 : WM_BN;                   // keys of a tile one warp multiplies
+    constexpr int WK = KS ? 16 : BN;                   // keys of a tile one warp multiplies
     extern __shared__ __align__(16) unsigned char wm_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);       // [BM][KSTR]
     __nv_bfloat16* Ks = Qs + BM * KSTR;                                  // [2][64][KSTR]
-    __nv_bfloat16* Vs = Ks + 2 * WM_BN * KSTR;                           // [2][64][VSTR]
+    __nv_bfloat16* Vs = Ks + 2 * BN * KSTR;                           // [2][64][VSTR]
     const int s = blockIdx.y, rep = H / G;
     const int g = blockIdx.z / splits, split = blockIdx.z - g * splits;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
@@ -244,7 +286,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     const int i_lo = row0 / rep, i_hi = min(sp.qlen - 1, (row0 + BM - 1) / rep);
     const int kmax = first + i_hi + 1;
     const int kmin = window > 0 ? max(0, first + i_lo - window + 1) : 0;
-    int t_lo = kmin / WM_BN, t_hi = (kmax + WM_BN - 1) / WM_BN;          // key tiles [t_lo, t_hi)
+    int t_lo = kmin / BN, t_hi = (kmax + BN - 1) / BN;          // key tiles [t_lo, t_hi)
     if (splits > 1) {
         const int nt = t_hi - t_lo;
         const int a = t_lo + (int)(((int64_t)nt * split) / splits), b = t_lo + (int)(((int64_t)nt * (split + 1)) / splits);
@@ -256,20 +298,20 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     // a tile's rows: eight lanes copy one cache row (128 contiguous bytes per step), sixteen rows per pass.  The page numbers of a
     // tile are looked up one tile ahead of its copies, so that the table read never stands between a warp and its next MMAs.
     const int lr = tid >> 3, lc = tid & 7;
-    auto lookup = [&](int t, int (&pg)[WM_BN / 16]) {
+    auto lookup = [&](int t, int (&pg)[BN / 16]) {
 #pragma unroll
-        for (int p = 0; p < WM_BN / 16; ++p) {
-            const int j = t * WM_BN + p * 16 + lr;
+        for (int p = 0; p < BN / 16; ++p) {
+            const int j = t * BN + p * 16 + lr;
             pg[p] = (t < t_hi && j < kmax) ? bt[bs_shift >= 0 ? j >> bs_shift : j / block_size] : -1;
         }
     };
-    auto load_tile = [&](int buf, int t, const int (&pg)[WM_BN / 16]) {
-        const int j0 = t * WM_BN;
-        __nv_bfloat16* kd = Ks + buf * WM_BN * KSTR;
-        __nv_bfloat16* vd = Vs + buf * WM_BN * VSTR;
+    auto load_tile = [&](int buf, int t, const int (&pg)[BN / 16]) {
+        const int j0 = t * BN;
+        __nv_bfloat16* kd = Ks + buf * BN * KSTR;
+        __nv_bfloat16* vd = Vs + buf * BN * VSTR;
         constexpr int KC = DK / 8, VC = DV / 8;
 #pragma unroll
-        for (int p = 0; p < WM_BN / 16; ++p) {
+        for (int p = 0; p < BN / 16; ++p) {
             const int r = p * 16 + lr;
             const int j = j0 + r;
             const bool ok = pg[p] >= 0;
@@ -283,7 +325,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
         }
         wm_commit();
     };
-    int pg[WM_BN / 16];
+    int pg[BN / 16];
     lookup(t_lo, pg);
     if (t_lo < t_hi) load_tile(0, t_lo, pg);
     lookup(t_lo + 1, pg);
@@ -344,10 +386,10 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             wm_wait<0>();
         }
         __syncthreads();
-        const int j0 = t * WM_BN + wkey;                                 // first key this warp multiplies
+        const int j0 = t * BN + wkey;                                 // first key this warp multiplies
         if (w_hi >= j0 && w_lo < j0 + WK) {                              // warp-uniform: some row of this warp sees some key of its share
-            const __nv_bfloat16* kt = Ks + buf * WM_BN * KSTR + wkey * KSTR;
-            const __nv_bfloat16* vt = Vs + buf * WM_BN * VSTR + wkey * VSTR;
+            const __nv_bfloat16* kt = Ks + buf * BN * KSTR + wkey * KSTR;
+            const __nv_bfloat16* vt = Vs + buf * BN * VSTR + wkey * VSTR;
             float sc[WK / 8][4];
 #pragma unroll
             for (int n = 0; n < WK / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
@@ -558,21 +600,21 @@ __global__ void window_merge_kernel(const float* __restrict__ part, const int32_
     }
 }
 
-template <int DK, int DV, bool KS, bool QREG>
+template <int DK, int DV, bool KS, bool QREG, int BN>
 int launch_window_mma_as(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
                          int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
                          const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
                          float* part, cudaStream_t stream) {
     using bf = __nv_bfloat16;
     constexpr int BM = KS ? 16 : WM_BM;
-    const size_t smem = sizeof(bf) * ((size_t)BM * (DK + 8) + 2 * (size_t)WM_BN * (DK + 8) + 2 * (size_t)WM_BN * (DV + 8));
-    int rc = wa_ensure_smem(window_attn_mma_kernel<DK, DV, KS, QREG>, smem);
+    const size_t smem = sizeof(bf) * ((size_t)BM * (DK + 8) + 2 * (size_t)BN * (DK + 8) + 2 * (size_t)BN * (DV + 8));
+    int rc = wa_ensure_smem(window_attn_mma_kernel<DK, DV, KS, QREG, BN>, smem);
     if (rc != B200_OK) return rc;
     int bs_shift = -1;
     if ((block_size & (block_size - 1)) == 0)
         for (bs_shift = 0; (1 << bs_shift) < block_size; ++bs_shift) {}
     dim3 grid((max_q * (H / G) + BM - 1) / BM, num_seqs, G * splits);
-    B200_LAUNCH((window_attn_mma_kernel<DK, DV, KS, QREG>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
+    B200_LAUNCH((window_attn_mma_kernel<DK, DV, KS, QREG, BN>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
                 static_cast<const bf*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, bs_shift, cu_q, cu_k, ctx_lens,
                 slopes, window, static_cast<bf*>(out), H, G, scale, splits, part);
     rc = b200_launch_status(nullptr);
@@ -587,11 +629,12 @@ int launch_window_mma(const void* q, int64_t q_stride, const void* cache, int ro
                       const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
                       float* part, cudaStream_t stream) {
     if (cu_q == nullptr && H / G <= 16)                   // single-token step: the four warps share every key tile
-        return launch_window_mma_as<DK, DV, true, true>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
+        return launch_window_mma_as<DK, DV, true, true, 64>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
                                                   ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
     // row-tiled form: query fragments are re-read from shared memory per key tile (measured faster than 32 more live registers)
-    return launch_window_mma_as<DK, DV, false, false>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                                      ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
+    // (32-key tiles, which let four CTAs instead of two share an SM at 128-wide heads, were measured and are not faster)
+    return launch_window_mma_as<DK, DV, false, false, 64>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                                          ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
 }
 
 }  // namespace
@@ -602,6 +645,14 @@ extern "C" int b200m_qk_norm_store(void* qkv, int64_t stride, int q_cols, int k_
     if (!qkv || n < 0 || q_cols < 0 || k_cols < 0 || v_cols < 0 || stride < q_cols + k_cols + v_cols) return B200_EINVAL;
     if (k_cols + v_cols > 0 && (!slots || !cache)) return B200_EINVAL;
     if (n == 0) return B200_OK;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(q_norm_w) |
+                           reinterpret_cast<uintptr_t>(k_norm_w);
+    if (!is32 && ptrs % 16 == 0 && stride % 8 == 0 && q_cols % 8 == 0 && k_cols % 8 == 0 && v_cols % 8 == 0) {
+        using bf = __nv_bfloat16;
+        B200_LAUNCH((qk_norm_store_vec_kernel), n, 256, 0, static_cast<cudaStream_t>(stream), static_cast<bf*>(qkv), stride, q_cols, k_cols,
+                    v_cols, static_cast<const bf*>(q_norm_w), static_cast<const bf*>(k_norm_w), slots, static_cast<bf*>(cache), eps);
+        return b200_launch_status(nullptr);
+    }
     B200M_DISPATCH(is32, B200_LAUNCH((qk_norm_store_kernel<T>), n, 256, 0, static_cast<cudaStream_t>(stream), static_cast<T*>(qkv),
                                      stride, q_cols, k_cols, v_cols, static_cast<const T*>(q_norm_w),
                                      static_cast<const T*>(k_norm_w), slots, static_cast<T*>(cache), eps));

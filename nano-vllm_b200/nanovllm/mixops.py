@@ -207,7 +207,7 @@ def qk_norm_store(qkv: torch.Tensor, q_cols: int, k_cols: int, v_cols: int, q_no
 
 def window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, block_size: int, spans: StepSpans,
                      heads: int, kv_heads: int, dim: int, vdim: int, scale: float, slopes: torch.Tensor | None = None,
-                     window: int = 0, fma: bool = False, splits: int | None = None, flags: int = 0) -> torch.Tensor:
+                     window: int = 0, fma: bool = False, splits: int | None = None) -> torch.Tensor:
     """q [n, >= heads * dim] (row-strided view), cache [slots, kv_heads * (dim + vdim)] -> [n, heads * vdim]."""
     n = q.shape[0]
     assert q.dim() == 2 and q.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == kv_heads * (dim + vdim)
@@ -226,7 +226,7 @@ def window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.T
     _call("b200m_window_attention", q.data_ptr(), q.stride(0), cache.data_ptr(), cache.shape[-1], kv_heads * dim,
           block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
           _p(slopes), int(window), out.data_ptr(), n, spans.num_seqs, spans.max_q, heads, kv_heads, dim, vdim, scale, is32,
-          int(fma) | flags, nsplit, _p(part), _stream())
+          int(fma), nsplit, _p(part), _stream())
     return out
 
 
