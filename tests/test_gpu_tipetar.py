@@ -155,7 +155,7 @@ def test_distance_bias_and_head_groups(dtype):
 
 @pytest.mark.parametrize("bs", [16, 64])
 @pytest.mark.parametrize("shape", [(8, 2, 64, 64, 70), (4, 4, 32, 32, 33), (16, 2, 128, 128, 500), (6, 2, 64, 32, 64), (3, 1, 12, 20, 9),
-                                   (5, 5, 8, 4, 0), (2, 1, 128, 64, 1), (12, 4, 32, 128, 129)])
+                                   (5, 5, 8, 4, 0), (2, 1, 128, 64, 1), (12, 4, 32, 128, 129), (40, 2, 32, 64, 150)])
 def test_attention_shapes_and_batches(shape, bs):
     """Head counts, head sizes and windows on every kernel path, three unequal sequences in one step (a long portion, a short one that
     starts mid-page, a single token), compared with each sequence alone in float64."""
